@@ -72,14 +72,14 @@ class Cache:
         self.state_groups: List[_StateGroup] = []
         self._kv_of: Dict[Tuple[int, str], Tuple[int, int]] = {}        # (cache id, key) -> (group, index in group)
         self._state_of: Dict[Tuple[int, str], Tuple[int, int]] = {}
-        self._views: Dict[Tuple[int, bool], LayerCache] = {}
+        self._views: Dict[tuple, LayerCache] = {}
         pin = self.device.type == "cuda"
         for cid in sorted(requests):
             for req in requests[cid]:
                 if isinstance(req, KVRequest):
-                    sig = (req.kv_heads, req.head_dim, req.window)
+                    sig = (req.kv_heads, req.head_dim, req.window, req.values)
                     gi = next((i for i, g in enumerate(self.kv_groups)
-                               if (g.request.kv_heads, g.request.head_dim, g.request.window) == sig), None)
+                               if (g.request.kv_heads, g.request.head_dim, g.request.window, g.request.values) == sig), None)
                     if gi is None:
                         self.kv_groups.append(_KVGroup(req, [], None, None, None, None,
                                                        IndexPool(self.n_pages, "cache page"),
@@ -103,7 +103,7 @@ class Cache:
         for g in self.kv_groups:
             shape = (len(g.layers), self.n_pages, g.request.kv_heads, PAGE, g.request.head_dim)
             g.k = torch.zeros(shape, dtype=dtype, device=self.device)
-            g.v = torch.zeros(shape, dtype=dtype, device=self.device)
+            g.v = torch.zeros(shape, dtype=dtype, device=self.device) if g.request.values else None
             g.table = torch.zeros((self.max_seqs, self.max_pages_per_seq), dtype=torch.int32, device=self.device)
             g.table_host = torch.zeros((self.max_seqs, self.max_pages_per_seq), dtype=torch.int32,
                                        pin_memory=pin)
@@ -115,7 +115,7 @@ class Cache:
     def bytes(self) -> int:
         n = 0
         for g in self.kv_groups:
-            n += 2 * g.k.numel() * g.k.element_size()
+            n += (2 if g.v is not None else 1) * g.k.numel() * g.k.element_size()
         for g in self.state_groups:
             n += g.data.numel() * g.data.element_size()
         return n
@@ -189,15 +189,17 @@ class Cache:
             g.dirty.clear()
 
     # ---- views ---------------------------------------------------------------------------------
-    def layer_view(self, cache_id: int, writes: bool = True) -> LayerCache:
-        view = self._views.get((cache_id, writes))
+    def layer_view(self, cache_id: int, writes: bool = True, kv_id: Optional[int] = None) -> LayerCache:
+        """What entry `cache_id` of the run order sees; with kv_id its keys and values are those of entry kv_id
+        (read without storing) while the fixed-size state stays its own."""
+        view = self._views.get((cache_id, writes, kv_id))
         if view is not None:
             return view
-        view = self._views[(cache_id, writes)] = LayerCache(writes=writes)
+        view = self._views[(cache_id, writes, kv_id)] = LayerCache(writes=writes, kv_writes=writes and kv_id is None)
         for (cid, key), (gi, li) in self._kv_of.items():
-            if cid == cache_id:
+            if cid == (cache_id if kv_id is None else kv_id):
                 g = self.kv_groups[gi]
-                view.kv[key] = KVView(g.k[li], g.v[li], g.table, g.request.window)
+                view.kv[key] = KVView(g.k[li], g.v[li] if g.v is not None else None, g.table, g.request.window)
         for (cid, key), (gi, li) in self._state_of.items():
             if cid == cache_id:
                 view.state[key] = self.state_groups[gi].data[li]

@@ -33,10 +33,7 @@ class ModelConfig:
     def from_dict(cls, raw: Dict[str, Any]) -> "ModelConfig":
         if not isinstance(raw, dict):
             raise ConfigError("config.json must hold a JSON object")
-        archs = raw.get("architectures")
-        if not (isinstance(archs, list) and archs and isinstance(archs[0], str)):
-            raise ConfigError("config.json: 'architectures' must be a non-empty list of strings")
-        kwargs: Dict[str, Any] = {"architecture": archs[0]}
+        kwargs: Dict[str, Any] = {"architecture": architecture_name(raw)}
         problems = []
         for f in fields(cls):
             if f.name == "architecture":
@@ -90,11 +87,20 @@ def lookup_architecture(name: str) -> Tuple[type, Callable]:
     return _ARCHITECTURES[name]
 
 
+def architecture_name(raw: Dict[str, Any]) -> str:
+    """The model's architecture: the first entry of 'architectures' (a list of strings), or 'architecture' (a string)."""
+    if not isinstance(raw, dict):
+        raise ConfigError("config.json must hold a JSON object")
+    archs = raw.get("architectures")
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        return archs[0]
+    if archs is None and isinstance(raw.get("architecture"), str) and raw["architecture"]:
+        return raw["architecture"]
+    raise ConfigError("config.json: 'architectures' must be a non-empty list of strings (or 'architecture' a string)")
+
+
 def config_from_dict(raw: Dict[str, Any]) -> ModelConfig:
-    archs = raw.get("architectures") if isinstance(raw, dict) else None
-    if not (isinstance(archs, list) and archs):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of strings")
-    config_cls, _ = lookup_architecture(archs[0])
+    config_cls, _ = lookup_architecture(architecture_name(raw))
     return config_cls.from_dict(raw)
 
 

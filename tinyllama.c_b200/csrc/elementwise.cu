@@ -312,10 +312,16 @@ extern "C" int tlc_gated_rmsnorm(const float* y, const float* y2, const void* z,
   return 0;
 }
 
-// ---- SwiGLU product: out = silu(gate) * up, gate|up side by side in one row ---------------
-// interleave: gate and up come in groups of 16 columns (8 gates, then their 8 ups) instead of as two halves
-template <typename TI, typename T>
-__global__ void swiglu_kernel(const TI* __restrict__ gu, int ld, int F, T* __restrict__ out, size_t total, int interleave) {
+// ---- gated product: out = act(gate) * up, gate|up side by side in one row -----------------
+// interleave: gate and up come in groups of 16 columns (8 gates, then their 8 ups) instead of as two halves.
+// ACT 0: SiLU; 1: the tanh form of GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+template <int ACT> __device__ __forceinline__ float glu_act(float z) { return ACT == 1 ? gelu_tanh_f(z) : silu_f(z); }
+
+template <typename TI, typename T, int ACT>
+__global__ void glu_kernel(const TI* __restrict__ gu, int ld, int F, T* __restrict__ out, size_t total, int interleave) {
   tlc_pdl(gu, out);
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
@@ -323,17 +329,133 @@ __global__ void swiglu_kernel(const TI* __restrict__ gu, int ld, int F, T* __res
   const int f = (int)(i % F);
   const int gc = interleave ? (f >> 3) * 16 + (f & 7) : f, uc = interleave ? gc + 8 : F + f;
   const float g = to_f32(gu[t * ld + gc]), u = to_f32(gu[t * ld + uc]);
-  out[i] = from_f32<T>(silu_f(g) * u);
+  out[i] = from_f32<T>(glu_act<ACT>(g) * u);
+}
+
+extern "C" int tlc_glu(const void* gu, int in_dtype, int ld, int F, int T, void* out, int dtype, int interleave, int act,
+                       cudaStream_t stream) {
+  const size_t total = (size_t)T * F;
+  if (total == 0) return 0;
+  TLC_REQUIRE(act == 0 || act == 1, "glu: unknown activation %d (0 SiLU, 1 GELU in its tanh form)", act);
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (act == 1) {
+    TLC_DISPATCH_DTYPE(in_dtype, TI, TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(glu_kernel<TI, TT, 1>, dim3(blocks), dim3(256), 0, stream,
+        (const TI*)gu, ld, F, (TT*)out, total, interleave)));
+  } else {
+    TLC_DISPATCH_DTYPE(in_dtype, TI, TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(glu_kernel<TI, TT, 0>, dim3(blocks), dim3(256), 0, stream,
+        (const TI*)gu, ld, F, (TT*)out, total, interleave)));
+  }
+  TLC_CHECK_LAUNCH("glu");
+  return 0;
 }
 
 extern "C" int tlc_swiglu(const void* gu, int in_dtype, int ld, int F, int T, void* out, int dtype, int interleave,
                           cudaStream_t stream) {
-  const size_t total = (size_t)T * F;
-  if (total == 0) return 0;
-  const unsigned blocks = (unsigned)((total + 255) / 256);
-  TLC_DISPATCH_DTYPE(in_dtype, TI, TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(swiglu_kernel<TI, TT>, dim3(blocks), dim3(256), 0, stream, 
-      (const TI*)gu, ld, F, (TT*)out, total, interleave)));
-  TLC_CHECK_LAUNCH("swiglu");
+  return tlc_glu(gu, in_dtype, ld, F, T, out, dtype, interleave, 0, stream);
+}
+
+// ---- RMSNorm with token shift --------------------------------------------------------------
+// n[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w;  out[t] = n[t] + (n[t-1] - n[t]) * mu, where n[t-1] is the normed row of
+// the sequence's previous token: the row above in this step, or what the sequence's slot of `state` [n_slots, D] holds
+// from its last step (zeros at position 0).  One block per row; it norms the row above by itself, and the block of a
+// sequence's first row of the step, which is the only one to read the slot, afterwards leaves the sequence's last normed
+// row there (every thread reads the elements it later writes).
+__device__ __forceinline__ float row_inv_rms(const float* xr, int D, float eps, float* red) {
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) { const float v = xr[d]; ss += v * v; }
+  ss = block_sum(ss, red);
+  return 1.0f / sqrtf(ss / (float)D + eps);
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+rmsnorm_shift_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ mu, float eps, int D,
+                     const int* __restrict__ row_seq, const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+                     const int* __restrict__ start_pos, float* state, TO* __restrict__ out) {
+  tlc_pdl(x, state, out);
+  __shared__ float red[33];
+  const int t = blockIdx.x, b = row_seq[t];
+  const int first = cu_seqlens[b], last = cu_seqlens[b + 1] - 1;
+  const float* xr = x + (size_t)t * D;
+  const float s = row_inv_rms(xr, D, eps, red);
+  if (t > first) {
+    const float* xp = xr - D;
+    const float sp = row_inv_rms(xp, D, eps, red);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      const float n = xr[d] * s * w[d], p = xp[d] * sp * w[d];
+      out[(size_t)t * D + d] = from_f32<TO>(n + (p - n) * mu[d]);
+    }
+    return;
+  }
+  float* st = state + (size_t)slots[b] * D;
+  const bool fresh = start_pos[b] == 0;
+  const float* xl = x + (size_t)last * D;
+  const float sl = last == t ? s : row_inv_rms(xl, D, eps, red);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const float n = xr[d] * s * w[d], p = fresh ? 0.f : st[d];
+    out[(size_t)t * D + d] = from_f32<TO>(n + (p - n) * mu[d]);
+    st[d] = xl[d] * sl * w[d];
+  }
+}
+
+extern "C" int tlc_rmsnorm_shift(const float* x, const float* w, const float* mu, float eps, int T, int D, const int* row_seq,
+                                 const int* cu_seqlens, const int* slots, const int* start_pos, float* state, void* out,
+                                 int out_dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(rmsnorm_shift_kernel<TO>, dim3(T), dim3(256), 0, stream, x, w, mu, eps, D, row_seq,
+                                               cu_seqlens, slots, start_pos, state, (TO*)out));
+  TLC_CHECK_LAUNCH("rmsnorm_shift");
+  return 0;
+}
+
+// ---- RMSNorm of a sublayer's output, added into the residual stream ---------------------------
+// y[t] = sum over p < n_parts of parts[t, p, :] (in this order) + g[t] * extra[t, :] (where extra is given), with
+// g[t] = gate[t * gate_ld], or its sigmoid;  res[t] (+)= y[t] / sqrt(mean(y[t]^2) + eps) * w, or y[t] itself where w is
+// NULL.  One block per row; the row is summed twice rather than kept.
+__global__ void __launch_bounds__(256)
+rmsnorm_add_kernel(const float* __restrict__ parts, int n_parts, const float* __restrict__ extra,
+                   const float* __restrict__ gate, int gate_ld, int gate_sigmoid, const float* __restrict__ w, float eps, int D,
+                   float* __restrict__ res, int accumulate) {
+  tlc_pdl(parts, extra, gate, res);
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const float* pr = parts + (size_t)t * n_parts * D;
+  const float* er = extra ? extra + (size_t)t * D : nullptr;
+  float g = 1.0f;
+  if (gate) {
+    g = gate[(size_t)t * gate_ld];
+    if (gate_sigmoid) g = 1.0f / (1.0f + expf(-g));
+  }
+  float s = 1.0f;
+  if (w) {
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      float y = 0.f;
+      for (int p = 0; p < n_parts; p++) y += pr[(size_t)p * D + d];
+      if (er) y = fmaf(g, er[d], y);
+      ss += y * y;
+    }
+    ss = block_sum(ss, red);
+    s = 1.0f / sqrtf(ss / (float)D + eps);
+  }
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float y = 0.f;
+    for (int p = 0; p < n_parts; p++) y += pr[(size_t)p * D + d];
+    if (er) y = fmaf(g, er[d], y);
+    const float v = w ? y * s * w[d] : y;
+    float* o = res + (size_t)t * D + d;
+    *o = accumulate ? *o + v : v;
+  }
+}
+
+extern "C" int tlc_rmsnorm_add(const float* parts, int n_parts, const float* extra, const float* gate, int gate_ld,
+                               int gate_sigmoid, const float* w, float eps, int T, int D, float* res, int accumulate,
+                               cudaStream_t stream) {
+  if (T == 0) return 0;
+  TLC_REQUIRE(n_parts >= 0 && (n_parts > 0 || extra != nullptr), "rmsnorm_add: nothing to add");
+  tlc_launch(rmsnorm_add_kernel, dim3(T), dim3(256), 0, stream, parts, n_parts, extra, gate, gate_ld, gate_sigmoid, w, eps, D, res,
+             accumulate);
+  TLC_CHECK_LAUNCH("rmsnorm_add");
   return 0;
 }
 

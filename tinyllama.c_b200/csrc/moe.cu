@@ -1,0 +1,220 @@
+// Mixture of experts: routing, and the experts' gated feed-forwards as grouped products.
+//
+// Routing (tlc_moe_route): a token's scores are s = sigmoid(router logits), 32-bit; its `top` experts are those with
+// the largest scores (the lowest index wins a tie); its weights are the chosen scores as they are.  The kernel also
+// sorts the (token, choice) pairs by expert -- counts, offsets, and for every expert the list of its pairs -- so that
+// each expert's rows form one contiguous range of a permutation; nothing goes through the host, so the same launches
+// serve any routing (and a captured graph).
+//
+// Experts (tlc_moe_gate_up, tlc_moe_down): the weight multiplies the expert's INPUT, expert(w h); gate and up are
+// linear, so W (w h) = w (W h) and the epilogue of the first product applies w in 32 bits: act(w g) * (w u).  The
+// second product writes every pair's result into its own row of [T, top, D]; the norm that follows adds a token's rows
+// in the order of its choices, so the sum does not depend on where other tokens went.
+//
+// Both products work on tiles of 32 sorted rows of ONE expert; the grid is an upper bound (pairs / 32 + experts in
+// use) and a block past the last tile returns.
+#include "common.cuh"
+
+#define MOE_TM 32
+
+// One block.  logits [T, ld] float (E router columns).  ids/wts [T*top]; order [T*top]: pair index (t * top + k) of every
+// sorted position; offsets [E+1]: first sorted position of every expert; tile_off [E+1]: first tile of every expert.
+__global__ void __launch_bounds__(1024)
+moe_route_kernel(const float* __restrict__ logits, int ld, int T, int E, int top, int* __restrict__ ids, float* __restrict__ wts,
+                 int* __restrict__ order, int* __restrict__ offsets, int* __restrict__ tile_off) {
+  tlc_pdl(logits, ids, wts, order, offsets, tile_off);
+  extern __shared__ int shi[];
+  int* count = shi;            // [E]
+  int* cursor = shi + E;       // [E]
+  for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int t = threadIdx.x; t < T; t += blockDim.x) {
+    const float* lr = logits + (size_t)t * ld;
+    float last = INFINITY;
+    int last_e = -1;
+    for (int k = 0; k < top; k++) {
+      // the largest logit below (last, last_e) in the order (value descending, index ascending)
+      float best = -INFINITY;
+      int be = -1;
+      for (int e = 0; e < E; e++) {
+        const float v = lr[e];
+        const bool after = v < last || (v == last && e > last_e);
+        if (after && (be < 0 || v > best)) { best = v; be = e; }
+      }
+      if (be < 0) be = 0;                      // (NaN logits: no order; keep indices valid)
+      ids[t * top + k] = be;
+      wts[t * top + k] = 1.0f / (1.0f + expf(-lr[be]));
+      atomicAdd(&count[be], 1);
+      last = lr[be];
+      last_e = be;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, tiles = 0;
+    for (int e = 0; e < E; e++) {
+      offsets[e] = o;
+      tile_off[e] = tiles;
+      cursor[e] = o;
+      o += count[e];
+      tiles += (count[e] + MOE_TM - 1) / MOE_TM;
+    }
+    offsets[E] = o;
+    tile_off[E] = tiles;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < T * top; i += blockDim.x) order[atomicAdd(&cursor[ids[i]], 1)] = i;
+}
+
+extern "C" int tlc_moe_route(const float* logits, int ld, int T, int E, int top, int* ids, float* wts, int* order, int* offsets,
+                             int* tile_off, cudaStream_t stream) {
+  if (T == 0) return 0;
+  TLC_REQUIRE(E >= 1 && top >= 1 && top <= E && E <= 4096, "moe_route: %d experts, %d chosen", E, top);
+  tlc_launch(moe_route_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), stream, logits, ld, T, E, top, ids, wts, order,
+             offsets, tile_off);
+  TLC_CHECK_LAUNCH("moe_route");
+  return 0;
+}
+
+// Which expert and which of its rows a tile covers: the last expert whose first tile is <= tile.
+__device__ __forceinline__ bool moe_tile(int tile, const int* __restrict__ tile_off, const int* __restrict__ offsets, int E,
+                                         int* expert, int* row0, int* rows) {
+  if (tile >= tile_off[E]) return false;
+  int lo = 0, hi = E - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (tile_off[mid] <= tile) lo = mid; else hi = mid - 1;
+  }
+  *expert = lo;
+  *row0 = offsets[lo] + (tile - tile_off[lo]) * MOE_TM;
+  *rows = min(MOE_TM, offsets[lo + 1] - *row0);
+  return true;
+}
+
+// act[i, f] = silu(w_i g) * (w_i u) for sorted position i, with g | u = Wgu[e] x[token(i)]; Wgu [E, 2F, D] (F gate rows,
+// then F up rows).  Tile: 32 rows x 32 features, both halves.
+#define MOE_TN 32
+#define MOE_TK 32
+template <typename TA, typename TW, typename TO, bool QUICK>
+__global__ void __launch_bounds__(256)
+moe_gate_up_kernel(const TA* __restrict__ x, int ldx, const TW* __restrict__ wgu, const int* __restrict__ order,
+                   const int* __restrict__ offsets, const int* __restrict__ tile_off, const float* __restrict__ wts, int E, int top,
+                   int F, int D, TO* __restrict__ act) {
+  tlc_pdl(x, order, offsets, tile_off, wts, act);
+  __shared__ float As[MOE_TK][MOE_TM + 1], Gs[MOE_TK][MOE_TN + 1], Us[MOE_TK][MOE_TN + 1];
+  __shared__ int tok[MOE_TM];
+  int e, row0, rows;
+  if (!moe_tile(blockIdx.x, tile_off, offsets, E, &e, &row0, &rows)) return;
+  const int n0 = blockIdx.y * MOE_TN;
+  if (threadIdx.x < MOE_TM) tok[threadIdx.x] = threadIdx.x < rows ? order[row0 + threadIdx.x] / top : -1;
+  __syncthreads();
+  const TW* wg = wgu + (size_t)e * 2 * F * D;
+  const TW* wu = wg + (size_t)F * D;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float g00 = 0.f, g01 = 0.f, g10 = 0.f, g11 = 0.f, u00 = 0.f, u01 = 0.f, u10 = 0.f, u11 = 0.f;
+  for (int k0 = 0; k0 < D; k0 += MOE_TK) {
+    for (int i = threadIdx.x; i < MOE_TM * MOE_TK; i += 256) {
+      const int rr = i / MOE_TK, kk = i % MOE_TK, k = k0 + kk;
+      const int tk = tok[rr];
+      As[kk][rr] = (tk >= 0 && k < D) ? to_f32(x[(size_t)tk * ldx + k]) : 0.f;
+      const int n = n0 + rr;
+      const bool ok = n < F && k < D;
+      Gs[kk][rr] = ok ? to_f32(wg[(size_t)n * D + k]) : 0.f;
+      Us[kk][rr] = ok ? to_f32(wu[(size_t)n * D + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < MOE_TK; kk++) {
+      const float a0 = As[kk][ty], a1 = As[kk][ty + 16];
+      const float p0 = Gs[kk][tx], p1 = Gs[kk][tx + 16], q0 = Us[kk][tx], q1 = Us[kk][tx + 16];
+      g00 = fmaf(a0, p0, g00); g01 = fmaf(a0, p1, g01); g10 = fmaf(a1, p0, g10); g11 = fmaf(a1, p1, g11);
+      u00 = fmaf(a0, q0, u00); u01 = fmaf(a0, q1, u01); u10 = fmaf(a1, q0, u10); u11 = fmaf(a1, q1, u11);
+    }
+    __syncthreads();
+  }
+  const int na = n0 + tx, nb = na + 16;
+  if (ty < rows) {
+    const float w = wts[order[row0 + ty]];
+    TO* o = act + (size_t)(row0 + ty) * F;
+    if (na < F) o[na] = from_f32<TO>(silu_of<QUICK>(w * g00) * (w * u00));
+    if (nb < F) o[nb] = from_f32<TO>(silu_of<QUICK>(w * g01) * (w * u01));
+  }
+  if (ty + 16 < rows) {
+    const float w = wts[order[row0 + ty + 16]];
+    TO* o = act + (size_t)(row0 + ty + 16) * F;
+    if (na < F) o[na] = from_f32<TO>(silu_of<QUICK>(w * g10) * (w * u10));
+    if (nb < F) o[nb] = from_f32<TO>(silu_of<QUICK>(w * g11) * (w * u11));
+  }
+}
+
+// y[pair(i), :] = Wd[e] act[i, :]; Wd [E, D, F]; y float [T*top, D].
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(256)
+moe_down_kernel(const TA* __restrict__ act, const TW* __restrict__ wd, const int* __restrict__ order,
+                const int* __restrict__ offsets, const int* __restrict__ tile_off, int E, int F, int D, float* __restrict__ y) {
+  tlc_pdl(act, order, offsets, tile_off, y);
+  __shared__ float As[MOE_TK][MOE_TM + 1], Ws[MOE_TK][MOE_TN + 1];
+  int e, row0, rows;
+  if (!moe_tile(blockIdx.x, tile_off, offsets, E, &e, &row0, &rows)) return;
+  const int n0 = blockIdx.y * MOE_TN;
+  const TW* w = wd + (size_t)e * D * F;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float c00 = 0.f, c01 = 0.f, c10 = 0.f, c11 = 0.f;
+  for (int k0 = 0; k0 < F; k0 += MOE_TK) {
+    for (int i = threadIdx.x; i < MOE_TM * MOE_TK; i += 256) {
+      const int rr = i / MOE_TK, kk = i % MOE_TK, k = k0 + kk;
+      As[kk][rr] = (rr < rows && k < F) ? to_f32(act[(size_t)(row0 + rr) * F + k]) : 0.f;
+      const int n = n0 + rr;
+      Ws[kk][rr] = (n < D && k < F) ? to_f32(w[(size_t)n * F + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < MOE_TK; kk++) {
+      const float a0 = As[kk][ty], a1 = As[kk][ty + 16], w0 = Ws[kk][tx], w1 = Ws[kk][tx + 16];
+      c00 = fmaf(a0, w0, c00); c01 = fmaf(a0, w1, c01); c10 = fmaf(a1, w0, c10); c11 = fmaf(a1, w1, c11);
+    }
+    __syncthreads();
+  }
+  const int na = n0 + tx, nb = na + 16;
+  if (ty < rows) {
+    float* o = y + (size_t)order[row0 + ty] * D;
+    if (na < D) o[na] = c00;
+    if (nb < D) o[nb] = c01;
+  }
+  if (ty + 16 < rows) {
+    float* o = y + (size_t)order[row0 + ty + 16] * D;
+    if (na < D) o[na] = c10;
+    if (nb < D) o[nb] = c11;
+  }
+}
+
+static inline int moe_max_tiles(int T, int E, int top) {
+  const long long pairs = (long long)T * top;
+  return (int)(pairs / MOE_TM + (pairs < E ? pairs : E));
+}
+
+extern "C" int tlc_moe_gate_up(const void* x, int x_dtype, int ldx, const void* wgu, int w_dtype, const int* order,
+                               const int* offsets, const int* tile_off, const float* wts, int T, int E, int top, int F, int D,
+                               void* act, int act_dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  dim3 grid(moe_max_tiles(T, E, top), (F + MOE_TN - 1) / MOE_TN);
+  if (act_dtype == TLC_BF16) {
+    TLC_DISPATCH_DTYPE(x_dtype, TA, TLC_DISPATCH_DTYPE(w_dtype, TW, tlc_launch(moe_gate_up_kernel<TA, TW, __nv_bfloat16, true>, grid,
+        dim3(256), 0, stream, (const TA*)x, ldx, (const TW*)wgu, order, offsets, tile_off, wts, E, top, F, D, (__nv_bfloat16*)act)));
+  } else {
+    TLC_DISPATCH_DTYPE(x_dtype, TA, TLC_DISPATCH_DTYPE(w_dtype, TW, tlc_launch(moe_gate_up_kernel<TA, TW, float, false>, grid,
+        dim3(256), 0, stream, (const TA*)x, ldx, (const TW*)wgu, order, offsets, tile_off, wts, E, top, F, D, (float*)act)));
+  }
+  TLC_CHECK_LAUNCH("moe_gate_up");
+  return 0;
+}
+
+extern "C" int tlc_moe_down(const void* act, int act_dtype, const void* wd, int w_dtype, const int* order, const int* offsets,
+                            const int* tile_off, int T, int E, int top, int F, int D, float* y, cudaStream_t stream) {
+  if (T == 0) return 0;
+  dim3 grid(moe_max_tiles(T, E, top), (D + MOE_TN - 1) / MOE_TN);
+  TLC_DISPATCH_DTYPE(act_dtype, TA, TLC_DISPATCH_DTYPE(w_dtype, TW, tlc_launch(moe_down_kernel<TA, TW>, grid, dim3(256), 0, stream,
+      (const TA*)act, (const TW*)wd, order, offsets, tile_off, E, F, D, y)));
+  TLC_CHECK_LAUNCH("moe_down");
+  return 0;
+}

@@ -75,6 +75,22 @@ int tlc_gated_rmsnorm(const float* y, const float* y2, const void* z, int z_dtyp
 int tlc_swiglu(const void* gu, int in_dtype, int ld, int F, int T, void* out, int dtype, int interleave,
                cudaStream_t stream);
 int tlc_gather_rows(const float* x, const int* rows, int R, int D, float* out, cudaStream_t stream);
+/* out[T, F] = act(gate) * up as tlc_swiglu; act 0: SiLU, 1: GELU in its tanh form. */
+int tlc_glu(const void* gu, int in_dtype, int ld, int F, int T, void* out, int dtype, int interleave, int act,
+            cudaStream_t stream);
+/* RMSNorm with token shift: n[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w and out[t] = n[t] + (n[t-1] - n[t]) * mu, with
+ * n[t-1] the normed row of the sequence's previous token: the row above in this step, or what the sequence's slot of
+ * state [n_slots, D] holds from its last step (zeros at position 0).  The slot then receives the sequence's last normed
+ * row of this step.  x float [T, D]; w, mu float [D]. */
+int tlc_rmsnorm_shift(const float* x, const float* w, const float* mu, float eps, int T, int D, const int* row_seq,
+                      const int* cu_seqlens, const int* slots, const int* start_pos, float* state, void* out,
+                      int out_dtype, cudaStream_t stream);
+/* res[t] (+)= y[t] / sqrt(mean(y[t]^2) + eps) * w (w NULL: y[t] itself) with y[t] = sum over p < n_parts of
+ * parts[t, p, :] + g[t] * extra[t, :]; parts float [T, n_parts, D] (NULL with n_parts 0), extra float [T, D] or NULL,
+ * g[t] = gate[t * gate_ld] (its sigmoid with gate_sigmoid; 1 with gate NULL), res float [T, D]. */
+int tlc_rmsnorm_add(const float* parts, int n_parts, const float* extra, const float* gate, int gate_ld,
+                    int gate_sigmoid, const float* w, float eps, int T, int D, float* res, int accumulate,
+                    cudaStream_t stream);
 
 /* ---- linear layers (gemm_tcgen05.cu, gemm_simt.cu) ----------------------------------------------------
  * out[m, n] (+)= (sum_k a[m, k] w[n, k]) * colscale[n] + colbias[n];  a [M, K], w [N, K], 32-bit sums.
@@ -205,6 +221,52 @@ int tlc_ssm_scan_ssd(const void* xbc, const float* dt, const float* A, const flo
                      float* scratch, const int* seg_start, const int* seg_seq, const int* seq_seg_start,
                      const int* slots, const int* start_pos, float* y, float* y_part, int* used_part, int B, int n_seg,
                      int T, int Hs, int P, int N, int G, int Cd, cudaStream_t stream, cudaStream_t aux);
+
+/* ---- attention over a shared latent (latent_attention.cu) -----------------------------------------------
+ * A token's cache row is [c | kr] (R normed latent values, r rotated key values that all heads share); pages
+ * [n_pages, TLC_PAGE, R + r].  tlc_latent_prepare reads a row's projections (float, row stride ld: H heads of
+ * (dn | r) query values at q_off; R + r down-projected values at dkv_off, or dkv_off < 0 for a layer that reads
+ * another layer's rows), writes the unrotated query parts to qn [T, H*dn], the rotated ones (interleaved pairs of the
+ * first `rot` dimensions, angle = position * inv_freq[i]) into the last r columns of every head of qa [T, H*(R+r)],
+ * and the row [rmsnorm(c) * cw | rotated kr] into its page.  qn, qa and pages are of `dtype`. */
+int tlc_latent_prepare(const float* proj, int ld, int q_off, int dkv_off, const float* cw, float eps,
+                       const float* inv_freq, int rot, const int* positions, const int* row_seq, const int* slots,
+                       const int* block_table, int max_pages, void* pages, void* qn, void* qa, int dtype, int T, int H,
+                       int dn, int r, int R, cudaStream_t stream);
+/* out[t, h, :R] = sum_j p_j c_j over the keys 0..position of the row's sequence, p = softmax of (qa[t, h] . [c_j | kr_j])
+ * * scale together with the head's sink (float [H]), which enters the maximum and the denominator only. */
+int tlc_latent_attention(const void* qa, const void* pages, int dtype, const float* sink, const int* block_table,
+                         int max_pages, const int* positions, const int* row_seq, const int* slots, void* out, int T,
+                         int H, int R, int r, float scale, cudaStream_t stream);
+/* A product per head: out[t, h, n] = sum_k a[t, h, k] w[h, n, k]; a with row stride lda and head stride a_hs, w
+ * [H, N, K] dense, out with row stride ldo and head stride o_hs; 32-bit sums. */
+int tlc_linear_heads(const void* a, int a_dtype, int lda, int a_hs, const void* w, int w_dtype, void* out,
+                     int out_dtype, int ldo, int o_hs, int T, int H, int N, int K, cudaStream_t stream);
+
+/* ---- minGRU (recurrent.cu) ------------------------------------------------------------------------------
+ * Per channel c < W of every row: z = sigmoid(proj[z_off + c]), u = proj[u_off + c], cand = u + 1/2 (u >= 0) or
+ * sigmoid(u); S <- (1 - z) S + z cand from the slot's state [n_slots, W] (zero at position 0), which receives the
+ * last S; out[t, c] = S * silu(proj[g_off + c]).  With seg_start [n_seg + 1] and seq_seg_start [B + 1] (the step's
+ * chunk table) and scratch of 2 * n_seg * W floats the chunks run side by side (same result up to rounding);
+ * seg_start NULL: row by row. */
+int tlc_mingru_scan(const float* proj, int ld, int z_off, int u_off, int g_off, int W, float* state,
+                    const int* cu_seqlens, const int* slots, const int* start_pos, int B, void* out, int out_dtype,
+                    int out_ld, const int* seg_start, const int* seq_seg_start, int n_seg, float* scratch,
+                    cudaStream_t stream);
+
+/* ---- mixture of experts (moe.cu) ------------------------------------------------------------------------
+ * tlc_moe_route: logits float [T, ld] (E columns) -> per token its `top` experts by descending logit (lowest index
+ * first on ties) in ids [T*top] with weights wts = sigmoid(logit); order [T*top] lists the pairs (t * top + k) sorted
+ * by expert, offsets [E+1] every expert's first sorted position, tile_off [E+1] its first tile of 32 sorted rows. */
+int tlc_moe_route(const float* logits, int ld, int T, int E, int top, int* ids, float* wts, int* order, int* offsets,
+                  int* tile_off, cudaStream_t stream);
+/* act[i, :F] = silu(w g) * (w u) for sorted position i: g | u = wgu[e] x[token], wgu [E, 2F, D], w the pair's weight. */
+int tlc_moe_gate_up(const void* x, int x_dtype, int ldx, const void* wgu, int w_dtype, const int* order,
+                    const int* offsets, const int* tile_off, const float* wts, int T, int E, int top, int F, int D,
+                    void* act, int act_dtype, cudaStream_t stream);
+/* y[pair, :D] = wd[e] act[i, :] for sorted position i of pair (t, k); wd [E, D, F]; y float [T*top, D]. */
+int tlc_moe_down(const void* act, int act_dtype, const void* wd, int w_dtype, const int* order, const int* offsets,
+                 const int* tile_off, int T, int E, int top, int F, int D, float* y, cudaStream_t stream);
 
 /* ---- sampling (sampling.cu) ------------------------------------------------------------------------ */
 /* out[r] = first index of the maximum of logits[r].  work: NULL (one block a row), or 12 * R bytes, 8-byte

@@ -1,2 +1,3 @@
 from .model import Model  # noqa: F401
 from . import falcon_h1  # noqa: F401  (registers FalconH1ForCausalLM)
+from . import turevik  # noqa: F401  (registers Turevik)

@@ -13,7 +13,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from .. import ops
-from ..parts.base import (ChunkRequest, LayerCache, LayerRun, LayerSpec, Part, PartSpec, StateRequest, StepInfo, WeightSpec,
+from ..parts.base import (ChunkRequest, KVRequest, LayerCache, LayerRun, LayerSpec, Part, PartSpec, StateRequest, StepInfo, WeightSpec,
                           step_scratch)
 from ..parts.block import Block
 from ..parts.linear import StackedLinear, matrix_dtype
@@ -36,6 +36,13 @@ class Model:
             if run.cache is not None and any(isinstance(q, StateRequest) for q in self.layers[run.layer].cache_requests()):
                 raise ValueError(f"run-order entry {r} reads the cache of entry {run.cache} but layer {run.layer} has a "
                                  f"mixer with state of its own: only keys and values can be read without storing")
+            if run.kv_cache is not None:
+                # keys and values of an EARLIER entry with a cache of its own: its rows of this step are stored
+                # before this entry reads them
+                if run.cache is not None or not (0 <= run.kv_cache < r) or self.schedule[run.kv_cache].cache is not None \
+                        or self.schedule[run.kv_cache].kv_cache is not None:
+                    raise ValueError(f"run-order entry {r} reads the keys and values of entry {run.kv_cache}, which must be "
+                                     f"an earlier entry that stores its own")
         # chunk lengths that parts want the step function to cut sequences into (one table each, every step)
         # as (rows, from how many rows of a sequence the table is wanted): the smallest threshold asked for a length
         asked: Dict[int, int] = {}
@@ -72,7 +79,14 @@ class Model:
 
     def cache_requests(self) -> Dict[int, list]:
         """Cache needs per entry of the run order that owns a cache (key: its index)."""
-        return {r: self.layers[run.layer].cache_requests() for r, run in enumerate(self.schedule) if run.cache is None}
+        out = {}
+        for r, run in enumerate(self.schedule):
+            if run.cache is None:
+                reqs = self.layers[run.layer].cache_requests()
+                if run.kv_cache is not None:          # its keys and values are another entry's
+                    reqs = [q for q in reqs if not isinstance(q, KVRequest)]
+                out[r] = reqs
+        return out
 
     def bind(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:
         self.dtype, self.device = dtype, torch.device(device)
@@ -98,7 +112,8 @@ class Model:
         ops.embed(step.tokens, self.embed_table, self.embed_scale, x)
         with step_scratch(step):                       # the layers share the step's temporaries
             for r, run in enumerate(self.schedule):
-                self.layers[run.layer].forward(x, step, cache.layer_view(r if run.cache is None else run.cache, run.writes))
+                self.layers[run.layer].forward(x, step, cache.layer_view(r if run.cache is None else run.cache, run.writes,
+                                                                         run.kv_cache))
         if want_rows is None or want_rows.numel() == 0:
             return None
         n = want_rows.numel()

@@ -91,6 +91,17 @@ _SIGNATURES = {
     "tlc_ssd_scratch_floats": (_ll, [_i, _i, _i, _i, _i, _i]),
     "tlc_ssm_scan_ssd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                               _i, _i, _vp, _vp]),
+    "tlc_glu": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp]),
+    "tlc_rmsnorm_shift": (_i, [_vp, _vp, _vp, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "tlc_rmsnorm_add": (_i, [_vp, _i, _vp, _vp, _i, _i, _vp, _f, _i, _i, _vp, _i, _vp]),
+    "tlc_latent_prepare": (_i, [_vp, _i, _i, _i, _vp, _f, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                                _vp]),
+    "tlc_latent_attention": (_i, [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
+    "tlc_linear_heads": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "tlc_mingru_scan": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _vp, _vp]),
+    "tlc_moe_route": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "tlc_moe_gate_up": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp]),
+    "tlc_moe_down": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
     "tlc_argmax": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "tlc_sample": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _f, _f, _f, _i, _f, _f, _vp, _vp]),
     "tlc_attention_decode_no_alloc": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
@@ -276,6 +287,69 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) 
         raise KernelError("swiglu: the interleaved layout needs a multiple of 8 features")
     _call("tlc_swiglu", gate_up.data_ptr(), dtype_code(gate_up.dtype), _rows(gate_up, "gate_up"), F, T,
           out.data_ptr(), dtype_code(out.dtype), int(bool(interleaved)), _stream())
+
+
+GLU_ACTS = {"silu": 0, "gelu_tanh": 1}
+
+
+def glu(gate_up: torch.Tensor, out: torch.Tensor, act: str = "silu", interleaved: bool = False) -> None:
+    """out = act(gate) * up with gate | up laid out as for swiglu; act: "silu" or "gelu_tanh"."""
+    _gpu(gate_up, out)
+    T, F2 = gate_up.shape
+    F = F2 // 2
+    if act not in GLU_ACTS:
+        raise KernelError(f"glu: unknown activation '{act}'; known: {sorted(GLU_ACTS)}")
+    if not out.is_contiguous() or tuple(out.shape) != (T, F) or F2 != 2 * F:
+        raise KernelError("glu: out must be contiguous [T, F]")
+    if interleaved and F % 8:
+        raise KernelError("glu: the interleaved layout needs a multiple of 8 features")
+    _call("tlc_glu", gate_up.data_ptr(), dtype_code(gate_up.dtype), _rows(gate_up, "gate_up"), F, T,
+          out.data_ptr(), dtype_code(out.dtype), int(bool(interleaved)), GLU_ACTS[act], _stream())
+
+
+def rmsnorm_shift(x: torch.Tensor, weight: torch.Tensor, mix: torch.Tensor, eps: float, state: torch.Tensor, step,
+                  out: torch.Tensor) -> None:
+    """n = rmsnorm(x) * weight; out[t] = n[t] + (n[t-1] - n[t]) * mix with n[t-1] the sequence's previous normed row:
+    the row above, or the slot's row of state [n_slots, D] (zeros at position 0), which then receives the sequence's
+    last normed row.  `step` is the StepInfo of the packed batch."""
+    _gpu(x, weight, mix, state, out)
+    T, D = x.shape
+    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous() or tuple(out.shape) != (T, D):
+        raise KernelError("rmsnorm_shift: x must be contiguous float32 [T, D] and out contiguous [T, D]")
+    _f32vec(weight, D, "rmsnorm_shift weight")
+    _f32vec(mix, D, "rmsnorm_shift mix")
+    if state.dtype != torch.float32 or not state.is_contiguous() or state.shape[-1] != D or state.dim() != 2:
+        raise KernelError("rmsnorm_shift: state must be contiguous float32 [n_slots, D]")
+    _call("tlc_rmsnorm_shift", x.data_ptr(), weight.data_ptr(), mix.data_ptr(), float(eps), T, D, step.row_seq.data_ptr(),
+          step.cu_seqlens.data_ptr(), step.slots.data_ptr(), step.start_pos.data_ptr(), state.data_ptr(), out.data_ptr(),
+          dtype_code(out.dtype), _stream())
+
+
+def rmsnorm_add(parts: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float, residual: torch.Tensor,
+                extra: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, gate_sigmoid: bool = False,
+                accumulate: bool = True) -> None:
+    """residual[t] (+)= rmsnorm(y[t]) * weight (weight None: y[t] itself) with y[t] = sum_p parts[t, p, :] + g[t] *
+    extra[t, :]; parts float32 [T, D] or [T, n, D], extra float32 [T, D], gate float32 [T] or one column of a wider
+    float32 matrix; g is the gate, or its sigmoid."""
+    _gpu(parts, weight, residual, extra, gate)
+    T, D = residual.shape
+    n = 0
+    if parts is not None:
+        n = 1 if parts.dim() == 2 else parts.shape[1]
+        if parts.dtype != torch.float32 or not parts.is_contiguous() or parts.numel() != T * n * D:
+            raise KernelError("rmsnorm_add: parts must be contiguous float32 [T, (n,) D]")
+    if extra is not None and (extra.dtype != torch.float32 or not extra.is_contiguous() or tuple(extra.shape) != (T, D)):
+        raise KernelError(f"rmsnorm_add: extra must be contiguous float32 {(T, D)}")
+    gate_ld = 0
+    if gate is not None:
+        if gate.dtype != torch.float32 or gate.dim() != 1 or gate.numel() != T:
+            raise KernelError("rmsnorm_add: gate must be float32 [T] (a column of a matrix will do)")
+        gate_ld = gate.stride(0) if T > 1 else 1
+    if residual.dtype != torch.float32 or not residual.is_contiguous():
+        raise KernelError("rmsnorm_add: the residual stream must be contiguous float32")
+    _f32vec(weight, D, "rmsnorm_add weight")
+    _call("tlc_rmsnorm_add", _p(parts), n, _p(extra), _p(gate), int(gate_ld), int(bool(gate_sigmoid)), _p(weight), float(eps),
+          T, D, residual.data_ptr(), int(bool(accumulate)), _stream())
 
 
 def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
@@ -731,3 +805,129 @@ def sample(logits: torch.Tensor, work: torch.Tensor, history: Optional[torch.Ten
     _call("tlc_sample", logits.data_ptr(), work.data_ptr(), _p(history), uniforms.data_ptr(), R, V,
           float(temperature), int(top_k), float(top_p), float(min_p), float(repeat_penalty), n_hist,
           float(frequency_penalty), float(presence_penalty), out.data_ptr(), _stream())
+
+
+# ---- attention over a shared latent -------------------------------------------------------------------
+MAX_LATENT = 512          # latent_attention.cu: 32 * LAT_MAXV values of a latent
+
+
+def latent_prepare(proj: torch.Tensor, q_off: int, dkv_off: Optional[int], norm_weight: Optional[torch.Tensor], eps: float,
+                   inv_freq: torch.Tensor, step, block_table: torch.Tensor, pages: torch.Tensor, qn: torch.Tensor,
+                   qa: torch.Tensor, H: int, dn: int, r: int, R: int) -> None:
+    """From a row's projections (float32 [T, *]: H heads of (dn | r) query values at q_off, R + r down-projected values
+    at dkv_off, None for a layer that reads another layer's rows): the unrotated query parts to qn [T, H*dn], the
+    rotated ones into the last r columns of every head of qa [T, H*(R+r)], and the cache row [rmsnorm(c) * norm_weight
+    | rotated kr] into its page of pages [n, 64, R+r].  The rotation turns interleaved pairs of the first
+    2 * len(inv_freq) dimensions."""
+    _gpu(proj, norm_weight, inv_freq, block_table, pages, qn, qa)
+    T = proj.shape[0]
+    _i32(block_table, "block_table")
+    if proj.dtype != torch.float32:
+        raise KernelError("latent_prepare: float32 projections")
+    if qn.dtype != pages.dtype or qa.dtype != pages.dtype or not qn.is_contiguous() or not qa.is_contiguous() \
+            or tuple(qn.shape) != (T, H * dn) or tuple(qa.shape) != (T, H * (R + r)):
+        raise KernelError("latent_prepare: qn [T, H*dn] and qa [T, H*(R+r)] must be contiguous and of the pages' type")
+    if not pages.is_contiguous() or tuple(pages.shape[1:]) != (PAGE, R + r):
+        raise KernelError("latent_prepare: pages must be contiguous [n, 64, R+r]")
+    if dkv_off is not None:
+        _f32vec(norm_weight, R, "latent norm weight")
+    _f32vec(inv_freq, inv_freq.numel(), "rotation inv_freq")
+    _call("tlc_latent_prepare", proj.data_ptr(), _rows(proj, "proj"), int(q_off), -1 if dkv_off is None else int(dkv_off),
+          _p(norm_weight), float(eps), inv_freq.data_ptr(), 2 * inv_freq.numel(), step.positions.data_ptr(),
+          step.row_seq.data_ptr(), step.slots.data_ptr(), block_table.data_ptr(), block_table.shape[1], pages.data_ptr(),
+          qn.data_ptr(), qa.data_ptr(), dtype_code(pages.dtype), T, H, dn, r, R, _stream())
+
+
+def latent_attention(qa: torch.Tensor, pages: torch.Tensor, sink: torch.Tensor, block_table: torch.Tensor, step,
+                     out: torch.Tensor, H: int, R: int, r: int, scale: float) -> None:
+    """out [T, H*R]: every head's softmax-weighted sum of the latents of keys 0..position, scores (qa . [c | kr]) * scale,
+    with the head's sink in the denominator."""
+    _gpu(qa, pages, sink, block_table, out)
+    T = qa.shape[0]
+    _i32(block_table, "block_table")
+    _f32vec(sink, H, "attention sink")
+    if qa.dtype != pages.dtype or out.dtype != pages.dtype or not qa.is_contiguous() or not out.is_contiguous() \
+            or tuple(qa.shape) != (T, H * (R + r)) or tuple(out.shape) != (T, H * R) or not pages.is_contiguous():
+        raise KernelError("latent_attention: qa [T, H*(R+r)] and out [T, H*R] contiguous and of the pages' type")
+    _call("tlc_latent_attention", qa.data_ptr(), pages.data_ptr(), dtype_code(pages.dtype), sink.data_ptr(),
+          block_table.data_ptr(), block_table.shape[1], step.positions.data_ptr(), step.row_seq.data_ptr(),
+          step.slots.data_ptr(), out.data_ptr(), T, H, R, r, float(scale), _stream())
+
+
+def linear_heads(a: torch.Tensor, a_head_stride: int, w: torch.Tensor, out: torch.Tensor, o_head_stride: int) -> None:
+    """out[t, h, n] = sum_k a[t, h, k] w[h, n, k]: w [H, N, K] contiguous; a and out are 2-D with dense rows, head h of a
+    row starting a_head_stride * h (o_head_stride * h) elements in."""
+    _gpu(a, w, out)
+    H, N, K = w.shape
+    T = a.shape[0]
+    if not w.is_contiguous() or out.shape[0] != T:
+        raise KernelError("linear_heads: w must be contiguous [H, N, K], a and out of equal rows")
+    lda, ldo = _rows(a, "linear_heads input"), _rows(out, "linear_heads output")
+    if (H - 1) * a_head_stride + K > max(lda, a.shape[1]) or (H - 1) * o_head_stride + N > max(ldo, out.shape[1]):
+        raise KernelError("linear_heads: a head lies outside its row")
+    _call("tlc_linear_heads", a.data_ptr(), dtype_code(a.dtype), lda, int(a_head_stride), w.data_ptr(), dtype_code(w.dtype),
+          out.data_ptr(), dtype_code(out.dtype), ldo, int(o_head_stride), T, H, N, K, _stream())
+
+
+# ---- minGRU ------------------------------------------------------------------------------------------------
+def mingru_scan(proj: torch.Tensor, z_off: int, u_off: int, g_off: int, width: int, state: torch.Tensor, step,
+                out: torch.Tensor, chunks=None) -> None:
+    """The gated recurrence S <- (1 - z) S + z cand of every sequence from its slot's state [n_slots, W] (zero at
+    position 0; updated in place), out[t] = S * silu(g); z, u, g are column ranges of proj (float32).  chunks: the
+    step's chunk table (seg_start, seg_seq, seq_seg_start) or None for the row-by-row form."""
+    _gpu(proj, state, out)
+    T = proj.shape[0]
+    if proj.dtype != torch.float32 or state.dtype != torch.float32 or not state.is_contiguous() or state.shape[-1] != width:
+        raise KernelError("mingru_scan: float32 projections and a contiguous float32 state [n_slots, W]")
+    out_ld = _out_rows(out, T, width, "mingru_scan")
+    seg = seq_seg = scratch = None
+    n_seg = 0
+    if chunks is not None:
+        seg, _, seq_seg = chunks
+        n_seg = seg.numel() - 1
+        scratch = torch.empty(2 * n_seg * width, dtype=torch.float32, device=proj.device)
+    _call("tlc_mingru_scan", proj.data_ptr(), _rows(proj, "proj"), int(z_off), int(u_off), int(g_off), int(width),
+          state.data_ptr(), step.cu_seqlens.data_ptr(), step.slots.data_ptr(), step.start_pos.data_ptr(), step.n_seqs,
+          out.data_ptr(), dtype_code(out.dtype), out_ld, _p(seg), _p(seq_seg), n_seg, _p(scratch), _stream())
+
+
+# ---- mixture of experts ------------------------------------------------------------------------------------
+def moe_route(logits: torch.Tensor, n_experts: int, top: int):
+    """Routing of every row of logits (float32 [T, >= E], the first E columns): returns (ids [T*top] int32, weights
+    [T*top] float32 = sigmoid of the chosen logits, order [T*top], offsets [E+1], tile_off [E+1]) as tlc_moe_route
+    describes them."""
+    _gpu(logits)
+    T = logits.shape[0]
+    if logits.dtype != torch.float32 or logits.shape[1] < n_experts:
+        raise KernelError("moe_route: float32 logits [T, >= E]")
+    dev = logits.device
+    ints = torch.empty(2 * T * top + 2 * (n_experts + 1), dtype=torch.int32, device=dev)
+    ids, order = ints[:T * top], ints[T * top:2 * T * top]
+    offsets = ints[2 * T * top:2 * T * top + n_experts + 1]
+    tile_off = ints[2 * T * top + n_experts + 1:]
+    wts = torch.empty(T * top, dtype=torch.float32, device=dev)
+    _call("tlc_moe_route", logits.data_ptr(), _rows(logits, "router logits"), T, int(n_experts), int(top), ids.data_ptr(),
+          wts.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_off.data_ptr(), _stream())
+    return ids, wts, order, offsets, tile_off
+
+
+def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, routing, top: int, act: torch.Tensor,
+                y: torch.Tensor) -> None:
+    """y[t, k, :] = expert_k(weight * x[t]) for every chosen (token, expert) pair: w_gate_up [E, 2F, D], w_down
+    [E, D, F]; act [T*top, F] is scratch of the activation type, y float32 [T, top, D]."""
+    _gpu(x, w_gate_up, w_down, act, y)
+    ids, wts, order, offsets, tile_off = routing
+    T, D = x.shape
+    E, F2, _ = w_gate_up.shape
+    F = F2 // 2
+    if not w_gate_up.is_contiguous() or not w_down.is_contiguous() or tuple(w_down.shape) != (E, D, F) \
+            or w_gate_up.shape[2] != D or w_gate_up.dtype != w_down.dtype:
+        raise KernelError("moe_experts: w_gate_up [E, 2F, D] and w_down [E, D, F] contiguous and of one type")
+    if not act.is_contiguous() or tuple(act.shape) != (T * top, F) or y.dtype != torch.float32 or not y.is_contiguous() \
+            or y.numel() != T * top * D:
+        raise KernelError("moe_experts: act [T*top, F] contiguous, y contiguous float32 [T, top, D]")
+    _call("tlc_moe_gate_up", x.data_ptr(), dtype_code(x.dtype), _rows(x, "moe input"), w_gate_up.data_ptr(),
+          dtype_code(w_gate_up.dtype), order.data_ptr(), offsets.data_ptr(), tile_off.data_ptr(), wts.data_ptr(), T, E, int(top),
+          F, D, act.data_ptr(), dtype_code(act.dtype), _stream())
+    _call("tlc_moe_down", act.data_ptr(), dtype_code(act.dtype), w_down.data_ptr(), dtype_code(w_down.dtype), order.data_ptr(),
+          offsets.data_ptr(), tile_off.data_ptr(), T, E, int(top), F, D, y.data_ptr(), _stream())

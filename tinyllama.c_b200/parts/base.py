@@ -10,7 +10,8 @@ choose a different mixer or feed-forward for every layer.
 
 Interfaces
 ----------
-Norm          forward(x32 [R, D] float32, out [R, D], rows=None)
+Norm          forward(x32 [R, D] float32, out [R, D], rows=None); add_normed(parts, residual, extra, gate) where it
+              serves as a sublayer's output norm; forward_step(x32, out, step, cache) where it keeps state (token shift)
 Position      rotation_table() -> inverse frequencies (the kernels rotate q and k themselves), or None and
               transform(qkv, q_off, k_off, step, n_heads, n_kv, head_dim): changes the q and k columns of
               the 32-bit projection in place; storing keys and values is the mixer's business
@@ -45,6 +46,8 @@ class KVRequest:
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    values: bool = True         # False: one row per position only (the "keys" pages); a mixer that derives its values
+                                # from the same row (a shared latent) asks for no second set of pages
 
 
 @dataclass(frozen=True)
@@ -100,7 +103,7 @@ class KVView:
     """One layer's pages of a key/value group: [n_pages, kv_heads, 64, head_dim] each, and the
     group's block table [n_slots, max_pages] (page index of every 64 positions of a slot)."""
     k_pages: torch.Tensor
-    v_pages: torch.Tensor
+    v_pages: Optional[torch.Tensor]          # None for a request without values
     block_table: torch.Tensor
     window: Optional[int] = None
 
@@ -111,6 +114,7 @@ class LayerCache:
     kv: Dict[str, KVView] = field(default_factory=dict)
     state: Dict[str, torch.Tensor] = field(default_factory=dict)     # [n_slots, *shape]
     writes: bool = True      # False: the layer reads another layer's cache and must not store into it
+    kv_writes: bool = True   # False: the keys/values here are another entry's (LayerRun.kv_cache); the state is this entry's own
 
 
 class Part:
@@ -195,11 +199,15 @@ class PartSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     """One layer as data: pre-mixer norm, mixers that run in parallel on the normed input and
-    add into the residual stream, pre-feed-forward norm, feed-forward."""
+    add into the residual stream, pre-feed-forward norm, feed-forward.  With an output norm a sublayer's result is
+    normed before it is added: x <- x + out_norm(sublayer(norm(x))).  A norm part that keeps per-sequence state (a token
+    shift) declares it like a mixer does."""
     mixer_norm: PartSpec
     mixers: Tuple[PartSpec, ...]
     ffn_norm: Optional[PartSpec]
     ffn: Optional[PartSpec]
+    mixer_out_norm: Optional[PartSpec] = None
+    ffn_out_norm: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
@@ -208,9 +216,12 @@ class LayerRun:
     may repeat (the weights are shared; every entry has a cache of its own, so a sequence's
     state is the same whether its tokens come at once or one by one).  ``cache`` names another
     entry of the run order (by its index) whose cache this entry reads instead, without
-    storing into it."""
+    storing into it.  ``kv_cache`` names an entry whose keys and values (only those) this entry
+    reads without storing, while it keeps fixed-size state of its own: a layer that attends over
+    what another layer cached."""
     layer: int
     cache: Optional[int] = None
+    kv_cache: Optional[int] = None
 
     @property
     def writes(self) -> bool:

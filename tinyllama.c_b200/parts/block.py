@@ -1,5 +1,6 @@
 """A layer: norm -> mixers in parallel on the same normed input -> residual; norm ->
-feed-forward -> residual.
+feed-forward -> residual.  With output norms (LayerSpec.mixer_out_norm, ffn_out_norm) a sublayer's
+result is collected in a 32-bit buffer of its own, normed, and then added.
 
 CodeClaper/tinyllama.c falcon_h1.c:311-395: n = norm(x); x = (x + attn(n)) + ssm(n);
 x = x + ffn(norm(x)).  The residual stream is 32-bit; each mixer and the feed-forward add
@@ -7,6 +8,7 @@ their output into it in the order they are listed.
 """
 from __future__ import annotations
 
+import inspect
 import os
 from typing import Dict, List, Optional
 
@@ -61,16 +63,23 @@ class Block(Part):
         self.mixers = [m.build() for m in spec.mixers]
         self.ffn_norm = spec.ffn_norm.build() if spec.ffn_norm is not None else None
         self.ffn = spec.ffn.build() if spec.ffn is not None else None
+        self.mixer_out_norm = spec.mixer_out_norm.build() if spec.mixer_out_norm is not None else None
+        self.ffn_out_norm = spec.ffn_out_norm.build() if spec.ffn_out_norm is not None else None
         self.dtype: Optional[torch.dtype] = None
+        # a part whose forward() takes `accumulate` can overwrite its target instead of adding into it
+        takes = lambda p: p is not None and "accumulate" in inspect.signature(p.forward).parameters
+        self._mixer_overwrites = [takes(m) for m in self.mixers]
+        self._ffn_overwrites = takes(self.ffn)
 
     def parts(self) -> List[Part]:
-        return [p for p in [self.mixer_norm, *self.mixers, self.ffn_norm, self.ffn] if p is not None]
+        return [p for p in [self.mixer_norm, *self.mixers, self.mixer_out_norm, self.ffn_norm, self.ffn, self.ffn_out_norm]
+                if p is not None]
 
     def weight_specs(self) -> List[WeightSpec]:
         return [s for p in self.parts() for s in p.weight_specs()]
 
     def cache_requests(self) -> list:
-        return [r for m in self.mixers for r in m.cache_requests()]
+        return [r for p in self.parts() for r in p.cache_requests()]
 
     def step_requests(self) -> list:
         return [r for p in self.parts() for r in p.step_requests()]
@@ -83,7 +92,7 @@ class Block(Part):
         # share one product: their input projections are stacked.  Any other mixer gets the normed
         # input as a tensor.
         self.fused_in, self.fused_offsets = None, []
-        if len(self.mixers) > 1 and all(hasattr(m, "input_projection") and hasattr(m, "forward_projected")
+        if len(self.mixers) > 1 and self.mixer_out_norm is None and all(hasattr(m, "input_projection") and hasattr(m, "forward_projected")
                                         for m in self.mixers):
             projs = [m.input_projection() for m in self.mixers]
             self.fused_in = StackedLinear.fuse_bound(projs)
@@ -181,11 +190,30 @@ class Block(Part):
         joint = scratch_buf("block.joint", (x32.shape[0], self.fused_out.in_features), self.dtype, x32.device)
         return joint, [joint[:, off:off + n] for off, n in self.out_offsets]
 
+    def _pre_norm(self, norm, x32: torch.Tensor, tag: str, step: StepInfo, cache: LayerCache) -> torch.Tensor:
+        normed = scratch_buf(tag, x32.shape, self.dtype, x32.device)
+        if hasattr(norm, "forward_step"):             # a norm with per-sequence state (token shift)
+            norm.forward_step(x32, normed, step, cache)
+        else:
+            norm.forward(x32, normed)
+        return normed
+
     def forward(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache) -> None:
         """Updates the float32 residual stream x32 [T, D] in place."""
-        if self.mixers:
-            normed = scratch_buf("block.normed", x32.shape, self.dtype, x32.device)
-            self.mixer_norm.forward(x32, normed)
+        if self.mixers and self.mixer_out_norm is not None:
+            # x <- x + out_norm(sum of the mixers' outputs)
+            normed = self._pre_norm(self.mixer_norm, x32, "block.normed", step, cache)
+            y = scratch_buf("block.mixed", x32.shape, torch.float32, x32.device)
+            if not self._mixer_overwrites[0]:
+                y.zero_()
+            for i, m in enumerate(self.mixers):
+                if self._mixer_overwrites[i]:
+                    m.forward(normed, step, cache, y, accumulate=i > 0)
+                else:
+                    m.forward(normed, step, cache, y)
+            self.mixer_out_norm.add_normed(y, x32)
+        elif self.mixers:
+            normed = self._pre_norm(self.mixer_norm, x32, "block.normed", step, cache)
             if self.fused_in is not None:
                 proj = scratch_buf("block.proj", (x32.shape[0], self.fused_in.out_features), torch.float32, x32.device)
                 self.fused_in.forward(normed, proj)
@@ -204,6 +232,18 @@ class Block(Part):
                 for m in self.mixers:
                     m.forward(normed, step, cache, x32)
         if self.ffn is not None:
-            normed = scratch_buf("block.ffn_normed", x32.shape, self.dtype, x32.device)
-            self.ffn_norm.forward(x32, normed)
-            self.ffn.forward(normed, x32)
+            normed = self._pre_norm(self.ffn_norm, x32, "block.ffn_normed", step, cache)
+            if self.ffn_out_norm is None:
+                self.ffn.forward(normed, x32)
+            elif hasattr(self.ffn, "forward_parts"):
+                # a feed-forward whose result is a sum of terms hands them to the norm, which adds them up itself
+                parts, extra, gate = self.ffn.forward_parts(normed)
+                self.ffn_out_norm.add_normed(parts, x32, extra, gate)
+            else:
+                y = scratch_buf("block.ffn_out", x32.shape, torch.float32, x32.device)
+                if self._ffn_overwrites:
+                    self.ffn.forward(normed, y, accumulate=False)
+                else:
+                    y.zero_()
+                    self.ffn.forward(normed, y)
+                self.ffn_out_norm.add_normed(y, x32)

@@ -1,32 +1,43 @@
-"""Dense gated feed-forward (SwiGLU).
+"""Dense gated feed-forward.
 
-d = W_down (silu(W_gate x) * (W_up x))  (CodeClaper/tinyllama.c falcon_h1.c:382-395).
-The gate and up projections are stacked into one product.  The multiplier on the gate's
-pre-activation, the one on the output, and the biases have no counterpart in the
-reference.
+d = W_down (act(W_gate x) * (W_up x)), act = SiLU (SwiGLU; CodeClaper/tinyllama.c
+falcon_h1.c:382-395) or another registered activation.  The gate and up projections are
+stacked into one product.  The multiplier on the gate's pre-activation, the one on the
+output, the biases, the choice of activation and of tensor names have no counterpart in
+the reference.
 """
 from __future__ import annotations
 
-from typing import Dict, List
+from typing import Dict, List, Optional
 
 import torch
 
 from .. import ops
-from .base import Part, WeightSpec, act_empty, register_feed_forward, scratch_buf
+from .base import Part, PartSpec, WeightSpec, act_empty, register_feed_forward, scratch_buf
 from .linear import StackedLinear
 
 
 @register_feed_forward("swiglu")
 class SwiGLU(Part):
     def __init__(self, hidden: int, intermediate: int, prefix: str, bias: bool = False, gate_scale: float = 1.0,
-                 down_scale: float = 1.0):
+                 down_scale: float = 1.0, act: str = "silu", names: Optional[Dict[str, str]] = None):
+        """act: "silu" or "gelu_tanh".  names: tensor names of gate, up, down after the prefix (default: the
+        gate_proj.weight / up_proj.weight / down_proj.weight of the architecture's checkpoints; biases, where asked
+        for, are those names with .bias for .weight)."""
         self.hidden, self.F = int(hidden), int(intermediate)
-        b = (lambda n: prefix + n + ".bias") if bias else (lambda n: None)
+        if act not in ops.GLU_ACTS:
+            raise ValueError(f"feed-forward: unknown activation '{act}'; known: {sorted(ops.GLU_ACTS)}")
+        self.act = act
+        nm = dict(gate="gate_proj.weight", up="up_proj.weight", down="down_proj.weight")
+        nm.update(names or {})
+        w = lambda n: prefix + nm[n]
+        b = (lambda n: prefix + (nm[n][:-len(".weight")] if nm[n].endswith(".weight") else nm[n]) + ".bias") if bias \
+            else (lambda n: None)
         self.gate_up = StackedLinear(hidden)
-        self.gate_up.add(prefix + "gate_proj.weight", self.F, b("gate_proj"), 1.0, gate_scale)
-        self.gate_up.add(prefix + "up_proj.weight", self.F, b("up_proj"))
+        self.gate_up.add(w("gate"), self.F, b("gate"), 1.0, gate_scale)
+        self.gate_up.add(w("up"), self.F, b("up"))
         self.down = StackedLinear(self.F)
-        self.down.add(prefix + "down_proj.weight", hidden, b("down_proj"), 1.0, down_scale)
+        self.down.add(w("down"), hidden, b("down"), 1.0, down_scale)
 
     def weight_specs(self) -> List[WeightSpec]:
         return self.gate_up.weight_specs() + self.down.weight_specs()
@@ -46,14 +57,91 @@ class SwiGLU(Part):
             if self.gate_up.colbias is not None:
                 self.gate_up.colbias = self.gate_up.colbias[idx].contiguous()
 
-    def forward(self, normed: torch.Tensor, residual: torch.Tensor) -> None:
+    def forward(self, normed: torch.Tensor, residual: torch.Tensor, accumulate: bool = True) -> None:
+        """Adds the result into `residual` (float32 [T, D]), or overwrites it with accumulate False."""
         T = normed.shape[0]
         act = scratch_buf("swiglu.act", (T, self.F), normed.dtype, normed.device)
-        if self.interleaved:
+        if self.interleaved and self.act == "silu":
             ops.linear_swiglu(normed, self.gate_up.weight, act, self.gate_up.colscale, self.gate_up.colbias)
         else:
             gu = scratch_buf("swiglu.gate_up", (T, 2 * self.F), torch.float32, normed.device)
             self.gate_up.forward(normed, gu)
-            ops.swiglu(gu, act)
-        self.down.forward(act, residual, accumulate=True)
+            ops.glu(gu, act, self.act, interleaved=self.interleaved)
+        self.down.forward(act, residual, accumulate=accumulate)
 
+
+
+@register_feed_forward("moe")
+class MoEFeedForward(Part):
+    """Mixture of experts with a sigmoid router.
+
+    Router scores s = sigmoid(W_router h) in 32 bits; each token takes the `top` experts with the largest scores, and
+    its weights are those scores as they are (not renormalised).  The weight multiplies the expert's INPUT: the result
+    is sum_e expert_e(s_e h), every expert a gated feed-forward W_down (silu(W_gate x) * (W_up x)) without biases.
+    Gate and up are linear, so the weight is applied to their 32-bit results.  An optional shared expert (a
+    feed-forward part of its own) runs on every token and is added times sigmoid(w_sg . h), one number per token; its
+    gate is computed with the router, as one more row of the router's matrix, in 32 bits.
+
+    The experts' weights are stacked [E, 2F, D] and [E, D, F]; rows are sorted by expert on the device, and every
+    (token, choice) pair's result gets a row of its own, which the norm that follows (or `forward`) adds in the order
+    of the token's choices: a token's result does not depend on what else is in the batch."""
+
+    def __init__(self, hidden: int, n_experts: int, top: int, expert_ff: int, router_name: str, expert_names: Dict[str, str],
+                 shared: Optional[PartSpec] = None, shared_gate_name: Optional[str] = None):
+        """expert_names: patterns of gate, up, down with {e} for the expert's index."""
+        self.hidden, self.E, self.top, self.F = int(hidden), int(n_experts), int(top), int(expert_ff)
+        if not (1 <= self.top <= self.E):
+            raise ValueError(f"moe: {self.top} of {self.E} experts cannot be chosen")
+        self.router_name, self.expert_names, self.shared_gate_name = router_name, dict(expert_names), shared_gate_name
+        self.shared = shared.build() if shared is not None else None
+        if (self.shared is None) != (shared_gate_name is None):
+            raise ValueError("moe: a shared expert and its gate come together")
+        self.dtype = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        specs = [WeightSpec(self.router_name, (self.E, self.hidden))]
+        for e in range(self.E):
+            n = {k: v.format(e=e) for k, v in self.expert_names.items()}
+            specs += [WeightSpec(n["gate"], (self.F, self.hidden)), WeightSpec(n["up"], (self.F, self.hidden)),
+                      WeightSpec(n["down"], (self.hidden, self.F))]
+        if self.shared is not None:
+            specs += self.shared.weight_specs() + [WeightSpec(self.shared_gate_name, (1, self.hidden))]
+        return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
+        from .linear import matrix_dtype
+        self.dtype = dtype
+        rows = [tensors[self.router_name]] + ([tensors[self.shared_gate_name]] if self.shared is not None else [])
+        self.router = torch.cat([r.to(device=device, dtype=torch.float32) for r in rows], dim=0).contiguous()   # 32-bit
+        names = [{k: v.format(e=e) for k, v in self.expert_names.items()} for e in range(self.E)]
+        mdt = torch.bfloat16
+        for n in names:
+            for k in ("gate", "up", "down"):
+                if matrix_dtype(tensors[n[k]].dtype, dtype) == torch.float32:
+                    mdt = torch.float32
+        to = lambda t: t.to(device=device, dtype=mdt)
+        self.w_gate_up = torch.stack([torch.cat([to(tensors[n["gate"]]), to(tensors[n["up"]])], dim=0) for n in names]).contiguous()
+        self.w_down = torch.stack([to(tensors[n["down"]]) for n in names]).contiguous()
+        if self.shared is not None:
+            self.shared.bind(tensors, dtype, device)
+
+    def forward_parts(self, normed: torch.Tensor):
+        """(parts float32 [T, top, D], shared expert's output float32 [T, D] or None, its gate's logit float32 [T] or
+        None): the result is sum_k parts[:, k] + sigmoid(logit) * shared."""
+        T, dev = normed.shape[0], normed.device
+        n_logits = self.router.shape[0]
+        logits = scratch_buf("moe.logits", (T, n_logits), torch.float32, dev)
+        ops.linear(normed, self.router, logits)
+        routing = ops.moe_route(logits, self.E, self.top)
+        act = scratch_buf("moe.act", (T * self.top, self.F), self.dtype, dev)
+        parts = scratch_buf("moe.parts", (T, self.top, self.hidden), torch.float32, dev)
+        ops.moe_experts(normed, self.w_gate_up, self.w_down, routing, self.top, act, parts)
+        if self.shared is None:
+            return parts, None, None
+        shared_out = scratch_buf("moe.shared", (T, self.hidden), torch.float32, dev)
+        self.shared.forward(normed, shared_out, accumulate=False)
+        return parts, shared_out, logits[:, self.E]          # the gate's logit: whoever adds the terms takes its sigmoid
+
+    def forward(self, normed: torch.Tensor, residual: torch.Tensor, accumulate: bool = True) -> None:
+        parts, extra, gate = self.forward_parts(normed)
+        ops.rmsnorm_add(parts, None, 0.0, residual, extra, gate, gate_sigmoid=True, accumulate=accumulate)

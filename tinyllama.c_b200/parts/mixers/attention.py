@@ -34,6 +34,9 @@ class AttentionMixer(Part):
         self.window = int(window) if window else None
         self.cache_key = cache_key
         self.position = position.build()
+        if getattr(self.position, "layout", "split_half") != "split_half":
+            raise ValueError(f"attention: the kernels of this mixer rotate split-half pairs; position part "
+                             f"'{position.name}' pairs dimensions as '{self.position.layout}'")
         b = (lambda n: prefix + n + ".bias") if bias else (lambda n: None)
         self.qkv = StackedLinear(hidden)
         self.q_off = self.qkv.add(prefix + "q_proj.weight", self.H * self.hd, b("q_proj"), in_scale)

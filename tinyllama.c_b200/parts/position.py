@@ -21,6 +21,8 @@ from .base import Position, register_position
 
 @register_position("rope_neox")
 class RotaryNeox(Position):
+    layout = "split_half"          # which dimensions form a pair: (i, i + r/2)
+
     def __init__(self, head_dim: int, theta: float, rope_dim: Optional[int] = None):
         self.head_dim = int(head_dim)
         self.rope_dim = int(rope_dim) if rope_dim else self.head_dim      # falcon_h1.c:265
@@ -37,6 +39,13 @@ class RotaryNeox(Position):
     def rotation_table(self) -> torch.Tensor:
         """The inverse frequencies (float32 [rope_dim/2]) for the kernels, which rotate by themselves."""
         return self.inv_freq
+
+
+@register_position("rope_interleaved")
+class RotaryInterleaved(RotaryNeox):
+    """The same angles with neighbours as pairs: dimensions (2i, 2i+1) of the first rope_dim turn by position *
+    theta^(-2i/rope_dim); (u, v) -> (u cos - v sin, v cos + u sin).  Only mixers whose kernels rotate this way take it."""
+    layout = "interleaved"
 
 
 @register_position("none")

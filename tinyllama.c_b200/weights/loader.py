@@ -109,6 +109,10 @@ def draw_tensor(spec, generator: torch.Generator, dtype: torch.dtype, std: float
         t = torch.empty(spec.shape, dtype=f32, device=dev).normal_(0.0, std, generator=generator).to(dtype)
     elif spec.init == "ones":
         t = (1.0 + torch.empty(spec.shape, dtype=f32, device=dev).normal_(0.0, norm_std, generator=generator)).to(dtype)
+    elif spec.init == "near_zero":
+        t = torch.empty(spec.shape, dtype=f32, device=dev).normal_(0.0, norm_std, generator=generator).to(dtype)
+    elif spec.init == "unit_interval":
+        t = torch.rand(spec.shape, generator=generator, dtype=f32, device=dev).to(dtype)
     elif spec.init == "zeros":
         t = torch.zeros(spec.shape, dtype=dtype, device=dev)
     elif spec.init == "a_log":
