@@ -35,3 +35,43 @@ TINY_D = dict(
     ssm_multipliers=[1.0, 0.5, 1.0, 1.0, 0.5], eos_token_id=3)
 
 ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+
+
+# ---- Turevik ---------------------------------------------------------------------------------------------------
+def _latent(heads, dim, rot_dim, vdim, kv_rank, scale, base=10000.0, dims=None, kv_from=None):
+    m = dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=kv_rank, scale=scale,
+             rot=dict(base=base, dims=rot_dim if dims is None else dims))
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return dict(type="latent_attention", mixer=m)
+
+
+def _moe(experts, top, ff, shared=None):
+    mlp = dict(kind="moe", router=dict(experts=experts, top=top), expert=dict(ff=ff))
+    if shared is not None:
+        mlp["shared"] = dict(ff=shared)
+    return mlp
+
+
+# A: a recurrent layer first; odd head counts (3, 5: the tensor-core kernel pads them); one layer whose rows are 56
+# wide (not a multiple of 16: the warp kernel also in bfloat16); two experts per token; a layer without feed-forward
+# that reads another layer's rows with other head sizes
+TUREVIK_A = dict(architecture="Turevik", vocab=160, width=64, norm=dict(eps=1e-5), layers=[
+    dict(type="mingru", mixer=dict(width=48), mlp=_moe(6, 2, 24, shared=40)),
+    dict(_latent(3, 8, 16, 24, 32, 0.3), mlp=dict(kind="dense", ff=96)),
+    dict(_latent(2, 16, 16, 8, 32, 0.2, kv_from=1), mlp=None),
+    dict(_latent(5, 24, 8, 16, 48, 0.25, base=500.0), mlp=_moe(5, 3, 16)),
+    dict(type="mingru", mixer=dict(width=80), mlp=dict(kind="dense", ff=40)),
+])
+
+# B: one head; all experts chosen; a single expert; fewer rotated dimensions than the rotated part is wide; widths that
+# are no multiples of 8
+TUREVIK_B = dict(architecture="Turevik", vocab=97, width=44, norm=dict(eps=1e-6), layers=[
+    dict(_latent(1, 12, 16, 12, 64, 0.5, base=100.0, dims=8), mlp=_moe(3, 3, 20, shared=12)),
+    dict(_latent(4, 4, 16, 20, 64, 0.35, base=100.0, dims=8, kv_from=0), mlp=_moe(1, 1, 28)),
+    dict(type="mingru", mixer=dict(width=52), mlp=None),
+    dict(_latent(8, 16, 32, 16, 96, 0.15), mlp=dict(kind="dense", ff=72)),
+    dict(_latent(2, 8, 32, 8, 96, 0.4, kv_from=3), mlp=_moe(7, 2, 12, shared=36)),
+])
+
+TUREVIK = {"TA": TUREVIK_A, "TB": TUREVIK_B}

@@ -182,3 +182,13 @@ def forward(cfg: dict, W: dict, tokens, rnd=_same, return_layers=False):
         after.append(x.copy())
     logits = rnd(offset_norm(x, W["final.norm"], eps)) @ rnd(np.asarray(W["embed"], dtype=np.float64)).T
     return (logits, np.stack(after)) if return_layers else logits
+
+
+def attend_latent(qa, rows, sink, scale, n_keys):
+    """One row's heads over cached rows [c | kr] directly in the latent space: qa [H, R + r], rows [n, R + r];
+    returns [H, R + r] = sum_j p_j rows_j (the first R columns are the heads' latent sums) with p the softmax of (qa . rows_j) * scale over j < n_keys and the head's sink."""
+    s = (qa @ rows[:n_keys].T) * scale                      # [H, n]
+    top = np.maximum(s.max(axis=1), sink)
+    e = np.exp(s - top[:, None])
+    den = e.sum(axis=1) + np.exp(sink - top)
+    return (e / den[:, None]) @ rows[:n_keys]

@@ -222,3 +222,308 @@ extern "C" int tlc_linear_heads(const void* a, int a_dtype, int lda, int a_hs, c
   TLC_CHECK_LAUNCH("linear_heads");
   return 0;
 }
+
+// ---- attention on the tensor cores (bfloat16 rows) -----------------------------------------------------------------
+// All heads of a row attend over the same cached rows, so (row, head) pairs are the M side of one product: a block takes
+// a tile of 64 pairs of ONE sequence -- HP heads (a power of two, H padded up to it, at most 64) of 64 / HP consecutive
+// rows -- and walks the sequence's pages.  A page [64 keys, R + r] arrives by cp.async (two in flight) and serves twice:
+// as the keys of S = Q K^T (all R + r columns) and as the values of O += P V (its first R columns, read transposed by
+// ldmatrix), so the cache is read once for both and once for all heads.  Four warps of 16 pairs each; scores, running
+// maximum and sum and the output accumulator are 32-bit registers, the softmax numerators that multiply the values are
+// bfloat16.  The key range of a tile may be cut into n_split ranges that run as blocks of their own (single-token steps,
+// pieces of long prompts) and leave (maximum, sum, unnormalised output) in 32-bit scratch; the merge adds them up and
+// brings in the head's sink, which enters the maximum and the denominator only.  With one range the block finishes the
+// rows itself.
+#define LT_M 64
+#define LT_KEYS TLC_PAGE
+__device__ __forceinline__ void lt_cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void lt_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void lt_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void lt_ldsm4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void lt_ldsm4_t(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void lt_mma(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t lt_pack(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// MAXNV: pairs of 8-column tiles of the output a thread may hold (R <= 16 * MAXNV).
+template <int MAXNV>
+__global__ void __launch_bounds__(128)
+latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfloat16* __restrict__ pages,
+                           const float* __restrict__ sink, const int* __restrict__ block_table, int max_pages,
+                           const int* __restrict__ cu_seqlens, const int* __restrict__ slots, const int* __restrict__ start_pos,
+                           __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int B, int H,
+                           int HP, int R, int r, float scale, int n_split) {
+  tlc_pdl(qa, pages, out, part_o, part_ml);
+  extern __shared__ __align__(16) unsigned char lt_smem[];
+  const int aw = R + r, ldsm = aw + 8;                    // padded row: ldmatrix rows land in different banks
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(lt_smem);
+  __nv_bfloat16* ks = qs + (size_t)LT_M * ldsm;           // two buffers of [64][ldsm]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, q4 = lane & 3;
+  const int rpt = LT_M / HP, n_hg = (H + HP - 1) / HP;    // rows per tile, head groups
+  // which sequence, rows and heads this tile covers
+  int tile = blockIdx.x / n_hg;
+  const int hg = blockIdx.x - tile * n_hg;
+  int b = 0, first = 0, len = 0;
+  for (; b < B; b++) {
+    first = cu_seqlens[b];
+    len = cu_seqlens[b + 1] - first;
+    const int nt = (len + rpt - 1) / rpt;
+    if (tile < nt) break;
+    tile -= nt;
+  }
+  if (b >= B) return;
+  const int row0 = tile * rpt, rows = min(rpt, len - row0);
+  const int t0 = first + row0, p0 = start_pos[b] + row0;  // first packed row and its position
+  const int h0 = hg * HP;
+  const int n_kt_all = (p0 + rows - 1) / LT_KEYS + 1;     // key tiles the tile's last row sees
+  const int split = blockIdx.y;
+  const int per = (n_kt_all + n_split - 1) / n_split;
+  const int kt0 = split * per, kt1 = min(n_kt_all, kt0 + per);
+  const int* table = block_table + (size_t)slots[b] * max_pages;
+  const uint32_t qs_u = (uint32_t)__cvta_generic_to_shared(qs), ks_u = (uint32_t)__cvta_generic_to_shared(ks);
+  const int chunks_row = aw >> 3;
+
+  auto load_keys = [&](int kt, int buf) {
+    const __nv_bfloat16* src = pages + (size_t)table[kt] * LT_KEYS * aw;
+    const uint32_t dst = ks_u + (uint32_t)buf * LT_KEYS * ldsm * 2;
+    for (int c = tid; c < LT_KEYS * chunks_row; c += 128) {
+      const int rr = c / chunks_row, cc = c - rr * chunks_row;
+      lt_cp_async16(dst + (uint32_t)(rr * ldsm + cc * 8) * 2, src + (size_t)rr * aw + cc * 8);
+    }
+  };
+  if (kt0 < kt1) {
+    // the tile's queries: pair m = row * HP + head; rows past the sequence and heads past H are zero
+    for (int c = tid; c < LT_M * chunks_row; c += 128) {
+      const int m = c / chunks_row, cc = c - m * chunks_row;
+      const int rl = m / HP, h = h0 + (m - rl * HP);
+      if (rl < rows && h < H)
+        lt_cp_async16(qs_u + (uint32_t)(m * ldsm + cc * 8) * 2, qa + ((size_t)(t0 + rl) * H + h) * aw + cc * 8);
+      else
+        *reinterpret_cast<uint4*>(qs + (size_t)m * ldsm + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    load_keys(kt0, 0);
+  }
+  lt_cp_commit();
+
+  const int nv = R >> 4;                                  // pairs of output tiles in use
+  float o[MAXNV][2][4];
+#pragma unroll
+  for (int i = 0; i < MAXNV; i++)
+#pragma unroll
+    for (int j = 0; j < 2; j++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) o[i][j][e] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int ma = warp * 16 + g, mb = ma + 8;              // this thread's two pairs
+  const int pos_a = p0 + ma / HP, pos_b = p0 + mb / HP;   // their positions (keys 0..pos are visible)
+  const float LOG2E = 1.4426950408889634f;
+
+  for (int kt = kt0; kt < kt1; kt++) {
+    const int buf = (kt - kt0) & 1;
+    if (kt + 1 < kt1) load_keys(kt + 1, buf ^ 1);
+    lt_cp_commit();
+    lt_cp_wait<1>();
+    __syncthreads();
+    const uint32_t kb = ks_u + (uint32_t)buf * LT_KEYS * ldsm * 2;
+    float s[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) s[j][e] = 0.f;
+    for (int k0 = 0; k0 < aw; k0 += 16) {
+      uint32_t a0, a1, a2, a3;
+      lt_ldsm4(a0, a1, a2, a3, qs_u + (uint32_t)((warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldsm + k0 + (lane >> 4) * 8) * 2);
+#pragma unroll
+      for (int jp = 0; jp < 4; jp++) {
+        uint32_t b0, b1, b2, b3;
+        lt_ldsm4(b0, b1, b2, b3, kb + (uint32_t)((jp * 16 + (lane & 7) + (lane >> 4) * 8) * ldsm + k0 + ((lane >> 3) & 1) * 8) * 2);
+        lt_mma(s[2 * jp], a0, a1, a2, a3, b0, b1);
+        lt_mma(s[2 * jp + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    // mask, scale, running maximum
+    const int key0 = kt * LT_KEYS + 2 * q4;
+    float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const int k = key0 + 8 * j;
+      s[j][0] = k <= pos_a ? s[j][0] * scale : -INFINITY;
+      s[j][1] = k + 1 <= pos_a ? s[j][1] * scale : -INFINITY;
+      s[j][2] = k <= pos_b ? s[j][2] * scale : -INFINITY;
+      s[j][3] = k + 1 <= pos_b ? s[j][3] * scale : -INFINITY;
+      mx_a = fmaxf(mx_a, fmaxf(s[j][0], s[j][1]));
+      mx_b = fmaxf(mx_b, fmaxf(s[j][2], s[j][3]));
+    }
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+    const float mn_a = fmaxf(m_run[0], mx_a), mn_b = fmaxf(m_run[1], mx_b);
+    const float ref_a = mn_a == -INFINITY ? 0.f : mn_a, ref_b = mn_b == -INFINITY ? 0.f : mn_b;
+    const float ca = exp2f((m_run[0] - ref_a) * LOG2E), cb = exp2f((m_run[1] - ref_b) * LOG2E);   // exp(-inf) = 0 at first
+    m_run[0] = mn_a;
+    m_run[1] = mn_b;
+    float sa = 0.f, sb = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      s[j][0] = exp2f((s[j][0] - ref_a) * LOG2E);
+      s[j][1] = exp2f((s[j][1] - ref_a) * LOG2E);
+      s[j][2] = exp2f((s[j][2] - ref_b) * LOG2E);
+      s[j][3] = exp2f((s[j][3] - ref_b) * LOG2E);
+      sa += s[j][0] + s[j][1];
+      sb += s[j][2] + s[j][3];
+    }
+    l_run[0] = l_run[0] * ca + sa;                        // (a thread's share; the quad's shares are added at the end)
+    l_run[1] = l_run[1] * cb + sb;
+#pragma unroll
+    for (int i = 0; i < MAXNV; i++)
+      if (i < nv) {
+#pragma unroll
+        for (int j = 0; j < 2; j++) { o[i][j][0] *= ca; o[i][j][1] *= ca; o[i][j][2] *= cb; o[i][j][3] *= cb; }
+      }
+    // O += P V: the numerators as bfloat16 A fragments, the page's first R columns as B
+#pragma unroll
+    for (int kk = 0; kk < 4; kk++) {
+      const uint32_t a0 = lt_pack(s[2 * kk][0], s[2 * kk][1]), a1 = lt_pack(s[2 * kk][2], s[2 * kk][3]);
+      const uint32_t a2 = lt_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = lt_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int i = 0; i < MAXNV; i++)
+        if (i < nv) {
+          uint32_t b0, b1, b2, b3;
+          lt_ldsm4_t(b0, b1, b2, b3, kb + (uint32_t)((kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldsm + i * 16 + (lane >> 4) * 8) * 2);
+          lt_mma(o[i][0], a0, a1, a2, a3, b0, b1);
+          lt_mma(o[i][1], a0, a1, a2, a3, b2, b3);
+        }
+    }
+    __syncthreads();                                       // the buffer is free for the tile after the next
+  }
+  lt_cp_wait<0>();
+  // the quad's shares of the sums
+#pragma unroll
+  for (int e = 0; e < 2; e++) {
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 1);
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 2);
+  }
+#pragma unroll
+  for (int e = 0; e < 2; e++) {
+    const int m = e == 0 ? ma : mb;
+    const int rl = m / HP, h = h0 + (m - rl * HP);
+    if (rl >= rows || h >= H) continue;
+    const size_t th = (size_t)(t0 + rl) * H + h;
+    if (n_split > 1) {
+      float* po = part_o + (th * n_split + split) * R;
+      if (q4 == 0) {
+        part_ml[(th * n_split + split) * 2] = m_run[e];
+        part_ml[(th * n_split + split) * 2 + 1] = l_run[e];
+      }
+#pragma unroll
+      for (int i = 0; i < MAXNV; i++)
+        if (i < nv) {
+#pragma unroll
+          for (int j = 0; j < 2; j++)
+            *reinterpret_cast<float2*>(po + i * 16 + j * 8 + 2 * q4) = make_float2(o[i][j][2 * e], o[i][j][2 * e + 1]);
+        }
+    } else {
+      const float sk = sink[h];
+      const float mf = fmaxf(m_run[e], sk);
+      const float w = exp2f((m_run[e] - mf) * LOG2E);
+      const float inv = w / (l_run[e] * w + exp2f((sk - mf) * LOG2E));
+      __nv_bfloat16* po = out + th * R;
+#pragma unroll
+      for (int i = 0; i < MAXNV; i++)
+        if (i < nv) {
+#pragma unroll
+          for (int j = 0; j < 2; j++)
+            *reinterpret_cast<uint32_t*>(po + i * 16 + j * 8 + 2 * q4) = lt_pack(o[i][j][2 * e] * inv, o[i][j][2 * e + 1] * inv);
+        }
+    }
+  }
+}
+
+// out[t, h, :] from the ranges' (maximum, sum, unnormalised output) and the head's sink.  A warp per (row, head).
+__global__ void __launch_bounds__(128)
+latent_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const float* __restrict__ sink,
+                              __nv_bfloat16* __restrict__ out, int TH, int H, int R, int n_split) {
+  tlc_pdl(part_o, part_ml, out);
+  const int th = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (th >= TH) return;
+  const float sk = sink[th % H];
+  const float* ml = part_ml + (size_t)th * n_split * 2;
+  float mf = sk;
+  for (int s = 0; s < n_split; s++) mf = fmaxf(mf, ml[2 * s]);
+  float den = expf(sk - mf);
+  for (int s = 0; s < n_split; s++) den += ml[2 * s + 1] * expf(ml[2 * s] - mf);     // an empty range: sum 0, exp(-inf) = 0
+  const float inv = 1.0f / den;
+  for (int d = lane; d < R; d += 32) {
+    float acc = 0.f;
+    for (int s = 0; s < n_split; s++) {
+      const float w = expf(ml[2 * s] - mf);
+      if (w > 0.f) acc = fmaf(part_o[((size_t)th * n_split + s) * R + d], w, acc);
+    }
+    out[(size_t)th * R + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+static int g_lt_smem_set = 0;
+extern "C" int tlc_latent_attention_tc_ok(int dtype, int H, int R, int r) {
+  if (dtype != TLC_BF16 || R % 16 || (R + r) % 16 || R > 256 || H < 1) return 0;
+  const size_t smem = (size_t)3 * LT_M * (R + r + 8) * 2;
+  return smem <= 200 * 1024 ? 1 : 0;
+}
+
+// How many ranges the keys of a tile are cut into: none while the tiles fill the GPU, else as many as bring the grid
+// to about two blocks an SM, at most one per page.
+extern "C" int tlc_latent_attention_tc_splits(int n_tiles, int max_keys) {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int pages = (max_keys + LT_KEYS - 1) / LT_KEYS;
+  if (n_tiles >= sms || pages <= 1) return 1;
+  int s = (2 * sms + n_tiles - 1) / n_tiles;
+  if (s > pages) s = pages;
+  if (s > 64) s = 64;
+  return s < 1 ? 1 : s;
+}
+
+extern "C" int tlc_latent_attention_tc(const void* qa, const void* pages, const float* sink, const int* block_table, int max_pages,
+                                       const int* cu_seqlens, const int* slots, const int* start_pos, void* out, float* part_o,
+                                       float* part_ml, int B, int T, int n_tiles, int H, int R, int r, float scale, int n_split,
+                                       cudaStream_t stream) {
+  if (T == 0) return 0;
+  TLC_REQUIRE(tlc_latent_attention_tc_ok(TLC_BF16, H, R, r), "latent_attention_tc: sizes H=%d R=%d r=%d are not built", H, R, r);
+  TLC_REQUIRE(n_split >= 1 && (n_split == 1 || (part_o && part_ml)), "latent_attention_tc: %d key ranges need scratch", n_split);
+  int HP = 1;
+  while (HP < H && HP < LT_M) HP <<= 1;
+  const int n_hg = (H + HP - 1) / HP;
+  const size_t smem = (size_t)3 * LT_M * (R + r + 8) * 2;
+  if (!g_lt_smem_set) {
+    cudaFuncSetAttribute(latent_attention_tc_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(latent_attention_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    g_lt_smem_set = 1;
+  }
+  dim3 grid(n_tiles * n_hg, n_split);
+  typedef const __nv_bfloat16* BP;
+  if (R <= 128)
+    tlc_launch(latent_attention_tc_kernel<8>, grid, dim3(128), smem, stream, (BP)qa, (BP)pages, sink, block_table, max_pages, cu_seqlens,
+               slots, start_pos, (__nv_bfloat16*)out, part_o, part_ml, B, H, HP, R, r, scale, n_split);
+  else
+    tlc_launch(latent_attention_tc_kernel<16>, grid, dim3(128), smem, stream, (BP)qa, (BP)pages, sink, block_table, max_pages, cu_seqlens,
+               slots, start_pos, (__nv_bfloat16*)out, part_o, part_ml, B, H, HP, R, r, scale, n_split);
+  TLC_CHECK_LAUNCH("latent_attention_tc");
+  if (n_split > 1) {
+    tlc_launch(latent_attention_merge_kernel, dim3((T * H + 3) / 4), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml,
+               sink, (__nv_bfloat16*)out, T * H, H, R, n_split);
+    TLC_CHECK_LAUNCH("latent_attention_merge");
+  }
+  return 0;
+}

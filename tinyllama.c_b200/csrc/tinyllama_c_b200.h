@@ -238,6 +238,18 @@ int tlc_latent_prepare(const float* proj, int ld, int q_off, int dkv_off, const 
 int tlc_latent_attention(const void* qa, const void* pages, int dtype, const float* sink, const int* block_table,
                          int max_pages, const int* positions, const int* row_seq, const int* slots, void* out, int T,
                          int H, int R, int r, float scale, cudaStream_t stream);
+/* The same on the tensor cores, for bfloat16 rows with R and R + r multiples of 16 and R <= 256 (tlc_..._ok): a block
+ * takes 64 (row, head) pairs of one sequence and reads every page once, as keys and as values.  Rows of a sequence are
+ * consecutive positions from start_pos.  n_tiles: an upper bound of the sum over sequences of ceil(rows / (64 / HP)),
+ * HP = H rounded up to a power of two (at most 64).  n_split > 1 cuts every tile's keys into that many ranges
+ * (tlc_..._splits proposes a number for `blocks` tiles and sequences of up to max_keys positions); part_o
+ * [T, H, n_split, R] and part_ml [T, H, n_split, 2] floats are then scratch. */
+int tlc_latent_attention_tc_ok(int dtype, int H, int R, int r);
+int tlc_latent_attention_tc_splits(int blocks, int max_keys);
+int tlc_latent_attention_tc(const void* qa, const void* pages, const float* sink, const int* block_table, int max_pages,
+                            const int* cu_seqlens, const int* slots, const int* start_pos, void* out, float* part_o,
+                            float* part_ml, int B, int T, int n_tiles, int H, int R, int r, float scale, int n_split,
+                            cudaStream_t stream);
 /* A product per head: out[t, h, n] = sum_k a[t, h, k] w[h, n, k]; a with row stride lda and head stride a_hs, w
  * [H, N, K] dense, out with row stride ldo and head stride o_hs; 32-bit sums. */
 int tlc_linear_heads(const void* a, int a_dtype, int lda, int a_hs, const void* w, int w_dtype, void* out,

@@ -97,6 +97,9 @@ _SIGNATURES = {
     "tlc_latent_prepare": (_i, [_vp, _i, _i, _i, _vp, _f, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                                 _vp]),
     "tlc_latent_attention": (_i, [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
+    "tlc_latent_attention_tc_ok": (_i, [_i, _i, _i, _i]),
+    "tlc_latent_attention_tc_splits": (_i, [_i, _i]),
+    "tlc_latent_attention_tc": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
     "tlc_linear_heads": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "tlc_mingru_scan": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _vp, _vp]),
     "tlc_moe_route": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
@@ -838,10 +841,22 @@ def latent_prepare(proj: torch.Tensor, q_off: int, dkv_off: Optional[int], norm_
           qn.data_ptr(), qa.data_ptr(), dtype_code(pages.dtype), T, H, dn, r, R, _stream())
 
 
+_latent_tc = not bool(int(os.environ.get("TLC_DISABLE_LATENT_TC", "0")))
+
+
+def latent_attention_tc(on: bool) -> None:
+    """Whether bfloat16 latent attention takes the tensor-core kernel where it is built (TLC_DISABLE_LATENT_TC=1 sets the
+    start value to off); for tests and comparisons."""
+    global _latent_tc
+    _latent_tc = bool(on)
+
+
 def latent_attention(qa: torch.Tensor, pages: torch.Tensor, sink: torch.Tensor, block_table: torch.Tensor, step,
-                     out: torch.Tensor, H: int, R: int, r: int, scale: float) -> None:
+                     out: torch.Tensor, H: int, R: int, r: int, scale: float, key_ranges: int = 0) -> None:
     """out [T, H*R]: every head's softmax-weighted sum of the latents of keys 0..position, scores (qa . [c | kr]) * scale,
-    with the head's sink in the denominator."""
+    with the head's sink in the denominator.  bfloat16 rows of sizes the tensor-core kernel is built for take it (all
+    heads of a row share every page read); key_ranges > 0 fixes into how many ranges it cuts a tile's keys (0: chosen:
+    more than one for few rows over many keys)."""
     _gpu(qa, pages, sink, block_table, out)
     T = qa.shape[0]
     _i32(block_table, "block_table")
@@ -849,6 +864,23 @@ def latent_attention(qa: torch.Tensor, pages: torch.Tensor, sink: torch.Tensor, 
     if qa.dtype != pages.dtype or out.dtype != pages.dtype or not qa.is_contiguous() or not out.is_contiguous() \
             or tuple(qa.shape) != (T, H * (R + r)) or tuple(out.shape) != (T, H * R) or not pages.is_contiguous():
         raise KernelError("latent_attention: qa [T, H*(R+r)] and out [T, H*R] contiguous and of the pages' type")
+    lib = library()
+    if _latent_tc and lib.tlc_latent_attention_tc_ok(dtype_code(pages.dtype), H, R, r):
+        hp = 1
+        while hp < H and hp < 64:
+            hp *= 2
+        B = step.n_seqs
+        n_tiles = T // (64 // hp) + B
+        n_split = key_ranges if key_ranges > 0 else lib.tlc_latent_attention_tc_splits(n_tiles * ((H + hp - 1) // hp),
+                                                                                         int(step.max_context))
+        part_o = part_ml = None
+        if n_split > 1:
+            part_o = torch.empty((T, H, n_split, R), dtype=torch.float32, device=qa.device)
+            part_ml = torch.empty((T, H, n_split, 2), dtype=torch.float32, device=qa.device)
+        _call("tlc_latent_attention_tc", qa.data_ptr(), pages.data_ptr(), sink.data_ptr(), block_table.data_ptr(),
+              block_table.shape[1], step.cu_seqlens.data_ptr(), step.slots.data_ptr(), step.start_pos.data_ptr(),
+              out.data_ptr(), _p(part_o), _p(part_ml), B, T, n_tiles, H, R, r, float(scale), int(n_split), _stream())
+        return
     _call("tlc_latent_attention", qa.data_ptr(), pages.data_ptr(), dtype_code(pages.dtype), sink.data_ptr(),
           block_table.data_ptr(), block_table.shape[1], step.positions.data_ptr(), step.row_seq.data_ptr(),
           step.slots.data_ptr(), out.data_ptr(), T, H, R, r, float(scale), _stream())
