@@ -135,7 +135,7 @@ def time_decode(llm, tlc, batch, prompt_len, steps, warmup, seed):
     from tinyllama_c_b200 import ops
     from tinyllama_c_b200.engine import EngineBackend, StepEntry
     g = torch.Generator().manual_seed(seed)
-    V = llm.config.vocab_size
+    V = llm.model.vocab
     slots = [llm.cache.acquire() for _ in range(batch)]
     prompts = torch.randint(0, V, (batch, prompt_len), generator=g).tolist()
     # prompts in groups that bound activation memory
@@ -177,7 +177,7 @@ def time_prefill(llm, T, seed, reps=3):
     best = None
     warm = 4                               # the first runs ramp the clocks and fill the tensor-map caches
     for r in range(reps + warm):
-        toks = torch.randint(0, llm.config.vocab_size, (T,), generator=g).tolist()
+        toks = torch.randint(0, llm.model.vocab, (T,), generator=g).tolist()
         s = llm.cache.acquire()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -245,6 +245,9 @@ def main() -> int:
     ap.add_argument("--no-big", dest="big", action="store_false", help="skip the 3B and 7B workloads among the points")
     ap.add_argument("--no-pairs", action="store_true", help="run the linear layers on single blocks (128 x 256 tiles) instead "
                     "of pairs of blocks on 256 x 256 tiles: the comparison behind profiles/linear_tcgen05_prefill_2048.md")
+    ap.add_argument("--design", default=None, choices=["turevik"], help="instead of the benchmark line: prefill and decode "
+                    "throughput of this design at layer sizes of a real model's order (random weights), beside Falcon-H1 at "
+                    "equal width and layer count")
     ap.add_argument("--ref-budget", type=float, default=600.0, help="seconds the reference arm may take (it runs fewer "
                     "layers, and says so, where all of them would take longer)")
     args = ap.parse_args()
@@ -254,6 +257,9 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU library")
         return 2
+
+    if args.design:
+        return design_compare(args)
 
     import torch
     import tinyllama_c_b200 as tlc
@@ -328,6 +334,88 @@ def main() -> int:
         torch.cuda.empty_cache()
         rec["points"].update(big_workloads(tlc, pk))
     print(json.dumps(rec))
+    return 0
+
+
+# ---- another design beside Falcon-H1 ---------------------------------------------------------------------------------
+def turevik_config(width, heads, kv_rank, ff, experts, top, expert_ff, shared_ff, gru, vocab):
+    """Four layers with every kind of sublayer: latent attention with rows of its own and a dense feed-forward; latent
+    attention over the first layer's rows and experts; minGRU and experts; latent attention and experts."""
+    att = lambda **kw: dict(type="latent_attention", mixer=dict(heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=kv_rank,
+                                                                scale=(128 + 64) ** -0.5, rot=dict(base=10000.0, dims=64), **kw))
+    moe = dict(kind="moe", router=dict(experts=experts, top=top), expert=dict(ff=expert_ff), shared=dict(ff=shared_ff))
+    return dict(architecture="Turevik", vocab=vocab, width=width, norm=dict(eps=1e-6), layers=[
+        dict(att(), mlp=dict(kind="dense", ff=ff)), dict(att(kv_from=0), mlp=moe),
+        dict(type="mingru", mixer=dict(width=gru), mlp=moe), dict(att(), mlp=moe)])
+
+
+def turevik_work(cfg, batch, context, T):
+    """(bytes a decode step of `batch` sequences at `context` must read, FLOPs of a prompt of T tokens)."""
+    D, V = cfg["width"], cfg["vocab"]
+    fixed, act_params, cache_bytes, att_flops = V * D, V * D, 0, 0.0
+    expert_bytes = 0.0
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "latent_attention":
+            H, dn, r, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            n = H * (dn + r) * D + H * dn * R + H * dv * R + D * H * dv + (0 if "kv_from" in m else (R + r) * D)
+            cache_bytes += batch * context * (R + r) * 2
+            att_flops += 2.0 * H * (2 * R + r) * T * (T + 1) / 2
+        else:
+            n = 4 * m["width"] * D
+        fixed += n
+        act_params += n
+        mlp = layer["mlp"]
+        if mlp["kind"] == "dense":
+            fixed += 3 * D * mlp["ff"]
+            act_params += 3 * D * mlp["ff"]
+        else:
+            E, top, F = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"]
+            shared = 3 * D * mlp["shared"]["ff"] + D
+            fixed += shared + E * D
+            act_params += shared + E * D + top * 3 * D * F
+            touched = E * (1.0 - (1.0 - 1.0 / E) ** (batch * top))          # expected distinct experts of a step
+            expert_bytes += touched * 3 * D * F * 2
+    return fixed * 2 + expert_bytes + cache_bytes, 2.0 * (act_params - V * D) * T + 2.0 * V * D + att_flops   # the head on one row
+
+
+def design_compare(args) -> int:
+    """Turevik beside Falcon-H1 at equal width and layer count: a prompt of --prefill-tokens tokens and decode steps at
+    batch 8 and 64 from --prompt-len-token prompts, each as time and as a fraction of the measured peak for the bytes a
+    step must read (decode) or the FLOPs a prompt needs (prefill)."""
+    import torch
+    import tinyllama_c_b200 as tlc
+    pk = peaks()
+    T, out = args.prefill_tokens, {}
+    cases = {
+        "width 2048": (turevik_config(2048, 16, 256, 4096, 32, 4, 1024, 1024, 4096, 65536), dict(CONFIG_1P5B, num_hidden_layers=4)),
+        "width 3072": (turevik_config(3072, 24, 256, 12288, 64, 6, 2048, 2048, 6144, 130048), dict(CONFIG_7B, num_hidden_layers=4)),
+    }
+    for name, (tcfg, fcfg) in cases.items():
+        for design, cfg in (("turevik", tcfg), ("falcon_h1", fcfg)):
+            model = tlc.random_model(cfg, seed=0, dtype="bfloat16")
+            llm = tlc.LLM(model, max_tokens=64 * (args.prompt_len + 2 * args.steps + 128) + T, max_seqs=64)
+            row = {}
+            pms = time_prefill(llm, T, seed=3)
+            ctx = args.prompt_len + args.steps // 2
+            if design == "turevik":
+                flops = turevik_work(cfg, 1, 0, T)[1]
+            else:
+                flops = prefill_flops(cfg, T)
+            row["prefill"] = {"tokens": T, "ms": round(pms, 3), "tok_s": round(T * 1000.0 / pms, 1),
+                              "frac_of_measured_bf16": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+            for batch in (8, 64):
+                ms, launches, clocks, ctx = time_decode(llm, tlc, batch, args.prompt_len, args.steps, args.warmup, seed=1)
+                nbytes = turevik_work(cfg, batch, ctx, 1)[0] if design == "turevik" else decode_bytes(cfg, batch, ctx)
+                row[f"decode_batch_{batch}"] = {"ms_per_step": round(ms, 4), "tok_s": round(batch * 1000.0 / ms, 1),
+                                                "launches_per_step": launches // args.steps,
+                                                "frac_of_measured_hbm": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+                                                "clocks": clocks}
+            out.setdefault(name, {})[design] = row
+            del llm, model
+            torch.cuda.empty_cache()
+    print(json.dumps({"design": args.design, "layers": 4, "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
+                      "peaks": pk, "sizes": out}))
     return 0
 
 

@@ -138,10 +138,10 @@ def test_unequal_batches_with_slots_and_pages_used_again(engines, folders, name,
     token at a time, the shorter ones end earlier and their slots and pages go to the next batch."""
     llm, folder = engines(name, dtype), folders[(name, dtype)]
     vocab = read_config(folder)["vocab"]
-    for round_ in range(3):
-        lens = [[1, 70, 140], [66, 3, 129, 20], [150, 64]][round_]
+    for wave in range(3):
+        lens = [[1, 70, 140], [66, 3, 129, 20], [150, 64]][wave]
         tail = [6, 3, 9, 1][:len(lens)]
-        reqs = [random_tokens(vocab, n + k, 400 + 10 * round_ + i) for i, (n, k) in enumerate(zip(lens, tail))]
+        reqs = [random_tokens(vocab, n + k, 400 + 10 * wave + i) for i, (n, k) in enumerate(zip(lens, tail))]
         slots = [llm.cache.acquire() for _ in reqs]
         got = [[] for _ in reqs]
         out = llm.step([StepEntry(s, q[:n], [n - 1]) for s, q, n in zip(slots, reqs, lens)]).cpu().numpy()
@@ -163,7 +163,7 @@ def test_unequal_batches_with_slots_and_pages_used_again(engines, folders, name,
         for i, q in enumerate(reqs):
             if slots[i] is not None:
                 llm.cache.release(slots[i])
-            check(np.stack(got[i]), folder, q, list(range(lens[i] - 1, len(q))), dtype, f"{name} batch {round_} request {i}")
+            check(np.stack(got[i]), folder, q, list(range(lens[i] - 1, len(q))), dtype, f"{name} batch {wave} request {i}")
         llm.cache.check()
 
 

@@ -121,12 +121,15 @@ def test_gated_activation(act):
     assert np.abs(out.cpu().numpy() - want).max() <= 2e-6 * np.abs(want).max()
 
 
-def test_product_per_head():
+@pytest.mark.parametrize("dtype,T,K,pad,N", [("float32", 45, 20, 5, 37), ("bfloat16", 45, 20, 5, 37), ("bfloat16", 1, 24, 8, 37),
+                                             ("bfloat16", 100, 72, 8, 70), ("bfloat16", 33, 16, 0, 64)])
+def test_product_per_head(dtype, T, K, pad, N):
+    """Heads that start inside wider rows; with 16-byte aligned bfloat16 rows the tensor-core kernel, else the CUDA cores."""
     g = np.random.default_rng(4)
-    T, H, K, N = 45, 3, 20, 37
-    a, w = g.standard_normal((T, H, K + 5)), g.standard_normal((H, N, K))
+    H = 3
+    a, w = draw(g, (T, H, K + pad), 1.0, dtype), draw(g, (H, N, K), 1.0, dtype)
     out = torch.zeros((T, H * (N + 2)), dtype=torch.float32, device="cuda")
-    ops.linear_heads(dev(a.reshape(T, -1)), K + 5, dev(w), out, N + 2)
+    ops.linear_heads(dev(a.reshape(T, -1), DT[dtype]), K + pad, dev(w, DT[dtype]), out, N + 2)
     want = np.einsum("thk,hnk->thn", a[:, :, :K], w)
     got = out.cpu().numpy().reshape(T, H, N + 2)
     assert np.abs(got[:, :, :N] - want).max() <= 1e-5 * np.abs(want).max()
@@ -308,11 +311,13 @@ def test_routing_ties_weights_and_every_experts_list():
         assert tile_off[e + 1] - tile_off[e] == (len(mine) + 31) // 32
 
 
-@pytest.mark.parametrize("dtype,E,top,shared", [("float32", 6, 2, 20), ("float32", 3, 1, None), ("float32", 40, 4, 12),
-                                                ("bfloat16", 5, 5, 20), ("bfloat16", 1, 1, None)])
-def test_experts_alone(dtype, E, top, shared):
+@pytest.mark.parametrize("dtype,E,top,shared,D,F", [("float32", 6, 2, 20, 44, 28), ("float32", 3, 1, None, 44, 28),
+                                                    ("float32", 40, 4, 12, 44, 28), ("bfloat16", 5, 5, 20, 44, 28),
+                                                    ("bfloat16", 1, 1, None, 44, 28), ("bfloat16", 5, 5, 24, 48, 40),
+                                                    ("bfloat16", 3, 3, None, 136, 72)])
+def test_experts_alone(dtype, E, top, shared, D, F):
+    """(Widths that are multiples of 8 in bfloat16: the tensor-core kernel; else the CUDA cores.)"""
     g = np.random.default_rng(10)
-    D, F = 44, 28
     mlp = dict(router=dict(experts=E, top=top), expert=dict(ff=F), shared=None if shared is None else dict(ff=shared))
     W = {"f.router": draw(g, (E, D), 0.5, dtype)}
     for e in range(E):

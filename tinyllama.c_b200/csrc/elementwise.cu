@@ -411,13 +411,14 @@ extern "C" int tlc_rmsnorm_shift(const float* x, const float* w, const float* mu
 // ---- RMSNorm of a sublayer's output, added into the residual stream ---------------------------
 // y[t] = sum over p < n_parts of parts[t, p, :] (in this order) + g[t] * extra[t, :] (where extra is given), with
 // g[t] = gate[t * gate_ld], or its sigmoid;  res[t] (+)= y[t] / sqrt(mean(y[t]^2) + eps) * w, or y[t] itself where w is
-// NULL.  One block per row; the row is summed twice rather than kept.
+// NULL.  One block per row; the summed row waits in shared memory for its scale where it fits, else it is summed twice.
 __global__ void __launch_bounds__(256)
 rmsnorm_add_kernel(const float* __restrict__ parts, int n_parts, const float* __restrict__ extra,
                    const float* __restrict__ gate, int gate_ld, int gate_sigmoid, const float* __restrict__ w, float eps, int D,
-                   float* __restrict__ res, int accumulate) {
+                   float* __restrict__ res, int accumulate, int keep) {
   tlc_pdl(parts, extra, gate, res);
   __shared__ float red[33];
+  extern __shared__ float yrow[];               // the summed row, where it fits (keep)
   const int t = blockIdx.x;
   const float* pr = parts + (size_t)t * n_parts * D;
   const float* er = extra ? extra + (size_t)t * D : nullptr;
@@ -433,15 +434,21 @@ rmsnorm_add_kernel(const float* __restrict__ parts, int n_parts, const float* __
       float y = 0.f;
       for (int p = 0; p < n_parts; p++) y += pr[(size_t)p * D + d];
       if (er) y = fmaf(g, er[d], y);
+      if (keep) yrow[d] = y;
       ss += y * y;
     }
     ss = block_sum(ss, red);
     s = 1.0f / sqrtf(ss / (float)D + eps);
   }
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float y = 0.f;
-    for (int p = 0; p < n_parts; p++) y += pr[(size_t)p * D + d];
-    if (er) y = fmaf(g, er[d], y);
+    float y;
+    if (w && keep) {
+      y = yrow[d];                              // (written by this thread)
+    } else {
+      y = 0.f;
+      for (int p = 0; p < n_parts; p++) y += pr[(size_t)p * D + d];
+      if (er) y = fmaf(g, er[d], y);
+    }
     const float v = w ? y * s * w[d] : y;
     float* o = res + (size_t)t * D + d;
     *o = accumulate ? *o + v : v;
@@ -453,8 +460,9 @@ extern "C" int tlc_rmsnorm_add(const float* parts, int n_parts, const float* ext
                                cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(n_parts >= 0 && (n_parts > 0 || extra != nullptr), "rmsnorm_add: nothing to add");
-  tlc_launch(rmsnorm_add_kernel, dim3(T), dim3(256), 0, stream, parts, n_parts, extra, gate, gate_ld, gate_sigmoid, w, eps, D, res,
-             accumulate);
+  const int keep = (size_t)D * sizeof(float) <= 40 * 1024;
+  tlc_launch(rmsnorm_add_kernel, dim3(T), dim3(256), keep ? (size_t)D * sizeof(float) : 0, stream, parts, n_parts, extra, gate, gate_ld,
+             gate_sigmoid, w, eps, D, res, accumulate, keep);
   TLC_CHECK_LAUNCH("rmsnorm_add");
   return 0;
 }

@@ -256,21 +256,23 @@ __device__ __forceinline__ uint32_t lt_pack(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// MAXNV: pairs of 8-column tiles of the output a thread may hold (R <= 16 * MAXNV).
-template <int MAXNV>
-__global__ void __launch_bounds__(128)
+// MAXNV: pairs of 8-column tiles of the output a thread may hold (R <= 16 * MAXNV).  NWARP: warps of 16 pairs each; a
+// prompt's tiles take 8 (128 pairs share every page that arrives), single-token steps 4.
+template <int MAXNV, int NWARP>
+__global__ void __launch_bounds__(NWARP * 32)
 latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bfloat16* __restrict__ pages,
                            const float* __restrict__ sink, const int* __restrict__ block_table, int max_pages,
                            const int* __restrict__ cu_seqlens, const int* __restrict__ slots, const int* __restrict__ start_pos,
                            __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int B, int H,
                            int HP, int R, int r, float scale, int n_split) {
   tlc_pdl(qa, pages, out, part_o, part_ml);
+  constexpr int LTM = NWARP * 16, NT = NWARP * 32;
   extern __shared__ __align__(16) unsigned char lt_smem[];
   const int aw = R + r, ldsm = aw + 8;                    // padded row: ldmatrix rows land in different banks
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(lt_smem);
-  __nv_bfloat16* ks = qs + (size_t)LT_M * ldsm;           // two buffers of [64][ldsm]
+  __nv_bfloat16* ks = qs + (size_t)LTM * ldsm;           // two buffers of [64][ldsm]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, q4 = lane & 3;
-  const int rpt = LT_M / HP, n_hg = (H + HP - 1) / HP;    // rows per tile, head groups
+  const int rpt = LTM / HP, n_hg = (H + HP - 1) / HP;    // rows per tile, head groups
   // which sequence, rows and heads this tile covers
   int tile = blockIdx.x / n_hg;
   const int hg = blockIdx.x - tile * n_hg;
@@ -297,14 +299,14 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bflo
   auto load_keys = [&](int kt, int buf) {
     const __nv_bfloat16* src = pages + (size_t)table[kt] * LT_KEYS * aw;
     const uint32_t dst = ks_u + (uint32_t)buf * LT_KEYS * ldsm * 2;
-    for (int c = tid; c < LT_KEYS * chunks_row; c += 128) {
+    for (int c = tid; c < LT_KEYS * chunks_row; c += NT) {
       const int rr = c / chunks_row, cc = c - rr * chunks_row;
       lt_cp_async16(dst + (uint32_t)(rr * ldsm + cc * 8) * 2, src + (size_t)rr * aw + cc * 8);
     }
   };
   if (kt0 < kt1) {
     // the tile's queries: pair m = row * HP + head; rows past the sequence and heads past H are zero
-    for (int c = tid; c < LT_M * chunks_row; c += 128) {
+    for (int c = tid; c < LTM * chunks_row; c += NT) {
       const int m = c / chunks_row, cc = c - m * chunks_row;
       const int rl = m / HP, h = h0 + (m - rl * HP);
       if (rl < rows && h < H)
@@ -451,13 +453,14 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bflo
   }
 }
 
-// out[t, h, :] from the ranges' (maximum, sum, unnormalised output) and the head's sink.  A warp per (row, head).
+// out[t, h, :] from the ranges' (maximum, sum, unnormalised output) and the head's sink.  A block per (row, head); a
+// thread per output column, all ranges' loads of a column in flight together.
 __global__ void __launch_bounds__(128)
 latent_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const float* __restrict__ sink,
-                              __nv_bfloat16* __restrict__ out, int TH, int H, int R, int n_split) {
+                              __nv_bfloat16* __restrict__ out, int H, int R, int n_split) {
   tlc_pdl(part_o, part_ml, out);
-  const int th = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (th >= TH) return;
+  __shared__ float wsh[64];
+  const int th = blockIdx.x;
   const float sk = sink[th % H];
   const float* ml = part_ml + (size_t)th * n_split * 2;
   float mf = sk;
@@ -465,13 +468,17 @@ latent_attention_merge_kernel(const float* __restrict__ part_o, const float* __r
   float den = expf(sk - mf);
   for (int s = 0; s < n_split; s++) den += ml[2 * s + 1] * expf(ml[2 * s] - mf);     // an empty range: sum 0, exp(-inf) = 0
   const float inv = 1.0f / den;
-  for (int d = lane; d < R; d += 32) {
+  if (threadIdx.x < n_split) wsh[threadIdx.x] = expf(ml[2 * threadIdx.x] - mf) * inv;
+  __syncthreads();
+  for (int d = threadIdx.x; d < R; d += blockDim.x) {
     float acc = 0.f;
+#pragma unroll 8
     for (int s = 0; s < n_split; s++) {
-      const float w = expf(ml[2 * s] - mf);
-      if (w > 0.f) acc = fmaf(part_o[((size_t)th * n_split + s) * R + d], w, acc);
+      const float w = wsh[s];
+      const float v = part_o[((size_t)th * n_split + s) * R + d];
+      acc = w > 0.f ? fmaf(v, w, acc) : acc;
     }
-    out[(size_t)th * R + d] = __float2bfloat16_rn(acc * inv);
+    out[(size_t)th * R + d] = __float2bfloat16_rn(acc);
   }
 }
 
@@ -480,6 +487,13 @@ extern "C" int tlc_latent_attention_tc_ok(int dtype, int H, int R, int r) {
   if (dtype != TLC_BF16 || R % 16 || (R + r) % 16 || R > 256 || H < 1) return 0;
   const size_t smem = (size_t)3 * LT_M * (R + r + 8) * 2;
   return smem <= 200 * 1024 ? 1 : 0;
+}
+
+// How many (row, head) pairs a tile takes: 128 for steps that bring several rows a sequence (where shared memory holds
+// such a tile beside two pages), else 64.
+extern "C" int tlc_latent_attention_tc_tile(int T, int B, int R, int r) {
+  const size_t smem = (size_t)(128 + 2 * LT_KEYS) * (R + r + 8) * 2;
+  return (T >= 4 * B && smem <= 200 * 1024) ? 128 : 64;
 }
 
 // How many ranges the keys of a tile are cut into: none while the tiles fill the GPU, else as many as bring the grid
@@ -497,32 +511,36 @@ extern "C" int tlc_latent_attention_tc_splits(int n_tiles, int max_keys) {
 
 extern "C" int tlc_latent_attention_tc(const void* qa, const void* pages, const float* sink, const int* block_table, int max_pages,
                                        const int* cu_seqlens, const int* slots, const int* start_pos, void* out, float* part_o,
-                                       float* part_ml, int B, int T, int n_tiles, int H, int R, int r, float scale, int n_split,
-                                       cudaStream_t stream) {
+                                       float* part_ml, int B, int T, int tile_pairs, int n_tiles, int H, int R, int r, float scale,
+                                       int n_split, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(tlc_latent_attention_tc_ok(TLC_BF16, H, R, r), "latent_attention_tc: sizes H=%d R=%d r=%d are not built", H, R, r);
-  TLC_REQUIRE(n_split >= 1 && (n_split == 1 || (part_o && part_ml)), "latent_attention_tc: %d key ranges need scratch", n_split);
+  TLC_REQUIRE(n_split >= 1 && n_split <= 64 && (n_split == 1 || (part_o && part_ml)), "latent_attention_tc: %d key ranges (1..64; more than one needs scratch)", n_split);
+  TLC_REQUIRE(tile_pairs == 64 || (tile_pairs == 128 && tlc_latent_attention_tc_tile(1 << 20, 1, R, r) == 128),
+              "latent_attention_tc: tiles of %d pairs are not built for R=%d r=%d", tile_pairs, R, r);
   int HP = 1;
-  while (HP < H && HP < LT_M) HP <<= 1;
+  while (HP < H && HP < 64) HP <<= 1;
   const int n_hg = (H + HP - 1) / HP;
-  const size_t smem = (size_t)3 * LT_M * (R + r + 8) * 2;
+  const size_t smem = (size_t)(tile_pairs + 2 * LT_KEYS) * (R + r + 8) * 2;
   if (!g_lt_smem_set) {
-    cudaFuncSetAttribute(latent_attention_tc_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    cudaFuncSetAttribute(latent_attention_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(latent_attention_tc_kernel<8, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(latent_attention_tc_kernel<16, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(latent_attention_tc_kernel<8, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(latent_attention_tc_kernel<16, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     g_lt_smem_set = 1;
   }
   dim3 grid(n_tiles * n_hg, n_split);
   typedef const __nv_bfloat16* BP;
-  if (R <= 128)
-    tlc_launch(latent_attention_tc_kernel<8>, grid, dim3(128), smem, stream, (BP)qa, (BP)pages, sink, block_table, max_pages, cu_seqlens,
-               slots, start_pos, (__nv_bfloat16*)out, part_o, part_ml, B, H, HP, R, r, scale, n_split);
-  else
-    tlc_launch(latent_attention_tc_kernel<16>, grid, dim3(128), smem, stream, (BP)qa, (BP)pages, sink, block_table, max_pages, cu_seqlens,
-               slots, start_pos, (__nv_bfloat16*)out, part_o, part_ml, B, H, HP, R, r, scale, n_split);
+#define LT_LAUNCH(NV, NW)                                                                                                      \
+  tlc_launch(latent_attention_tc_kernel<NV, NW>, grid, dim3(NW * 32), smem, stream, (BP)qa, (BP)pages, sink, block_table, max_pages, \
+             cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, part_o, part_ml, B, H, HP, R, r, scale, n_split)
+  if (tile_pairs == 128) { if (R <= 128) LT_LAUNCH(8, 8); else LT_LAUNCH(16, 8); }
+  else { if (R <= 128) LT_LAUNCH(8, 4); else LT_LAUNCH(16, 4); }
+#undef LT_LAUNCH
   TLC_CHECK_LAUNCH("latent_attention_tc");
   if (n_split > 1) {
-    tlc_launch(latent_attention_merge_kernel, dim3((T * H + 3) / 4), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml,
-               sink, (__nv_bfloat16*)out, T * H, H, R, n_split);
+    tlc_launch(latent_attention_merge_kernel, dim3(T * H), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml, sink,
+               (__nv_bfloat16*)out, H, R, n_split);
     TLC_CHECK_LAUNCH("latent_attention_merge");
   }
   return 0;

@@ -17,38 +17,44 @@
 
 #define MOE_TM 32
 
-// One block.  logits [T, ld] float (E router columns).  ids/wts [T*top]; order [T*top]: pair index (t * top + k) of every
-// sorted position; offsets [E+1]: first sorted position of every expert; tile_off [E+1]: first tile of every expert.
+// A thread per token: its `top` experts by descending logit (lowest index first on ties) and their weights.
+__global__ void __launch_bounds__(128)
+moe_topk_kernel(const float* __restrict__ logits, int ld, int T, int E, int top, int* __restrict__ ids, float* __restrict__ wts) {
+  tlc_pdl(logits, ids, wts);
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  const float* lr = logits + (size_t)t * ld;
+  float last = INFINITY;
+  int last_e = -1;
+  for (int k = 0; k < top; k++) {
+    // the largest logit below (last, last_e) in the order (value descending, index ascending)
+    float best = -INFINITY;
+    int be = -1;
+    for (int e = 0; e < E; e++) {
+      const float v = lr[e];
+      const bool after = v < last || (v == last && e > last_e);
+      if (after && (be < 0 || v > best)) { best = v; be = e; }
+    }
+    if (be < 0) be = 0;                      // (NaN logits: no order; keep indices valid)
+    ids[t * top + k] = be;
+    wts[t * top + k] = 1.0f / (1.0f + expf(-lr[be]));
+    last = lr[be];
+    last_e = be;
+  }
+}
+
+// One block sorts the pairs by expert: counts, offsets (and every expert's first tile of `tm` sorted rows), then the
+// list order [T*top]: pair index (t * top + k) of every sorted position.
 __global__ void __launch_bounds__(1024)
-moe_route_kernel(const float* __restrict__ logits, int ld, int T, int E, int top, int* __restrict__ ids, float* __restrict__ wts,
-                 int* __restrict__ order, int* __restrict__ offsets, int* __restrict__ tile_off) {
-  tlc_pdl(logits, ids, wts, order, offsets, tile_off);
+moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int E, int tm, int* __restrict__ order, int* __restrict__ offsets,
+                int* __restrict__ tile_off) {
+  tlc_pdl(ids, order, offsets, tile_off);
   extern __shared__ int shi[];
   int* count = shi;            // [E]
   int* cursor = shi + E;       // [E]
   for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
   __syncthreads();
-  for (int t = threadIdx.x; t < T; t += blockDim.x) {
-    const float* lr = logits + (size_t)t * ld;
-    float last = INFINITY;
-    int last_e = -1;
-    for (int k = 0; k < top; k++) {
-      // the largest logit below (last, last_e) in the order (value descending, index ascending)
-      float best = -INFINITY;
-      int be = -1;
-      for (int e = 0; e < E; e++) {
-        const float v = lr[e];
-        const bool after = v < last || (v == last && e > last_e);
-        if (after && (be < 0 || v > best)) { best = v; be = e; }
-      }
-      if (be < 0) be = 0;                      // (NaN logits: no order; keep indices valid)
-      ids[t * top + k] = be;
-      wts[t * top + k] = 1.0f / (1.0f + expf(-lr[be]));
-      atomicAdd(&count[be], 1);
-      last = lr[be];
-      last_e = be;
-    }
-  }
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&count[ids[i]], 1);
   __syncthreads();
   if (threadIdx.x == 0) {
     int o = 0, tiles = 0;
@@ -57,22 +63,24 @@ moe_route_kernel(const float* __restrict__ logits, int ld, int T, int E, int top
       tile_off[e] = tiles;
       cursor[e] = o;
       o += count[e];
-      tiles += (count[e] + MOE_TM - 1) / MOE_TM;
+      tiles += (count[e] + tm - 1) / tm;
     }
     offsets[E] = o;
     tile_off[E] = tiles;
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < T * top; i += blockDim.x) order[atomicAdd(&cursor[ids[i]], 1)] = i;
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) order[atomicAdd(&cursor[ids[i]], 1)] = i;
 }
 
 extern "C" int tlc_moe_route(const float* logits, int ld, int T, int E, int top, int* ids, float* wts, int* order, int* offsets,
                              int* tile_off, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(E >= 1 && top >= 1 && top <= E && E <= 4096, "moe_route: %d experts, %d chosen", E, top);
-  tlc_launch(moe_route_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), stream, logits, ld, T, E, top, ids, wts, order,
+  tlc_launch(moe_topk_kernel, dim3((T + 127) / 128), dim3(128), 0, stream, logits, ld, T, E, top, ids, wts);
+  TLC_CHECK_LAUNCH("moe_topk");
+  tlc_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), stream, (const int*)ids, T * top, E, MOE_TM, order,
              offsets, tile_off);
-  TLC_CHECK_LAUNCH("moe_route");
+  TLC_CHECK_LAUNCH("moe_sort");
   return 0;
 }
 

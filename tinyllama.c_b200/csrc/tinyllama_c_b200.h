@@ -239,17 +239,19 @@ int tlc_latent_attention(const void* qa, const void* pages, int dtype, const flo
                          int max_pages, const int* positions, const int* row_seq, const int* slots, void* out, int T,
                          int H, int R, int r, float scale, cudaStream_t stream);
 /* The same on the tensor cores, for bfloat16 rows with R and R + r multiples of 16 and R <= 256 (tlc_..._ok): a block
- * takes 64 (row, head) pairs of one sequence and reads every page once, as keys and as values.  Rows of a sequence are
- * consecutive positions from start_pos.  n_tiles: an upper bound of the sum over sequences of ceil(rows / (64 / HP)),
+ * takes tile_pairs (64 or 128) (row, head) pairs of one sequence and reads every page once, as keys and as values.  Rows of
+ * a sequence are consecutive positions from start_pos.  n_tiles: an upper bound of the sum over sequences of
+ * ceil(rows / (tile_pairs / HP)),
  * HP = H rounded up to a power of two (at most 64).  n_split > 1 cuts every tile's keys into that many ranges
  * (tlc_..._splits proposes a number for `blocks` tiles and sequences of up to max_keys positions); part_o
  * [T, H, n_split, R] and part_ml [T, H, n_split, 2] floats are then scratch. */
 int tlc_latent_attention_tc_ok(int dtype, int H, int R, int r);
 int tlc_latent_attention_tc_splits(int blocks, int max_keys);
+int tlc_latent_attention_tc_tile(int T, int B, int R, int r);      /* 64 or 128 pairs a tile (tile_pairs below) */
 int tlc_latent_attention_tc(const void* qa, const void* pages, const float* sink, const int* block_table, int max_pages,
                             const int* cu_seqlens, const int* slots, const int* start_pos, void* out, float* part_o,
-                            float* part_ml, int B, int T, int n_tiles, int H, int R, int r, float scale, int n_split,
-                            cudaStream_t stream);
+                            float* part_ml, int B, int T, int tile_pairs, int n_tiles, int H, int R, int r, float scale,
+                            int n_split, cudaStream_t stream);
 /* A product per head: out[t, h, n] = sum_k a[t, h, k] w[h, n, k]; a with row stride lda and head stride a_hs, w
  * [H, N, K] dense, out with row stride ldo and head stride o_hs; 32-bit sums. */
 int tlc_linear_heads(const void* a, int a_dtype, int lda, int a_hs, const void* w, int w_dtype, void* out,
@@ -279,6 +281,17 @@ int tlc_moe_gate_up(const void* x, int x_dtype, int ldx, const void* wgu, int w_
 /* y[pair, :D] = wd[e] act[i, :] for sorted position i of pair (t, k); wd [E, D, F]; y float [T*top, D]. */
 int tlc_moe_down(const void* act, int act_dtype, const void* wd, int w_dtype, const int* order, const int* offsets,
                  const int* tile_off, int T, int E, int top, int F, int D, float* y, cudaStream_t stream);
+
+/* ---- grouped products on the tensor cores (grouped_mma.cu) ----------------------------------------------
+ * mma.sync with bfloat16 operands for the product per head and for both expert products, where every operand row
+ * starts on a 16-byte boundary (tlc_grouped_mma_ok: a with row stride lda and group stride a_hs, w with rows of K).
+ * Same results as tlc_linear_heads / tlc_moe_gate_up + tlc_moe_down up to the order of the 32-bit sums. */
+int tlc_grouped_mma_ok(int a_dtype, int w_dtype, const void* a, int lda, int a_hs, const void* w, int K);
+int tlc_linear_heads_mma(const void* a, int lda, int a_hs, const void* w, void* out, int out_dtype, int ldo, int o_hs,
+                         int T, int H, int N, int K, cudaStream_t stream);
+int tlc_moe_experts_mma(const void* x, int ldx, const void* wgu, const void* wd, const int* order, const int* offsets,
+                        const int* tile_off, const float* wts, int T, int E, int top, int F, int D, void* act, float* y,
+                        cudaStream_t stream);
 
 /* ---- sampling (sampling.cu) ------------------------------------------------------------------------ */
 /* out[r] = first index of the maximum of logits[r].  work: NULL (one block a row), or 12 * R bytes, 8-byte

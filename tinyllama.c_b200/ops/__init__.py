@@ -99,8 +99,12 @@ _SIGNATURES = {
     "tlc_latent_attention": (_i, [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
     "tlc_latent_attention_tc_ok": (_i, [_i, _i, _i, _i]),
     "tlc_latent_attention_tc_splits": (_i, [_i, _i]),
-    "tlc_latent_attention_tc": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
+    "tlc_latent_attention_tc_tile": (_i, [_i, _i, _i, _i]),
+    "tlc_latent_attention_tc": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
     "tlc_linear_heads": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "tlc_grouped_mma_ok": (_i, [_i, _i, _vp, _i, _i, _vp, _i]),
+    "tlc_linear_heads_mma": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "tlc_moe_experts_mma": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
     "tlc_mingru_scan": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _vp, _vp]),
     "tlc_moe_route": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tlc_moe_gate_up": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp]),
@@ -870,20 +874,31 @@ def latent_attention(qa: torch.Tensor, pages: torch.Tensor, sink: torch.Tensor, 
         while hp < H and hp < 64:
             hp *= 2
         B = step.n_seqs
-        n_tiles = T // (64 // hp) + B
-        n_split = key_ranges if key_ranges > 0 else lib.tlc_latent_attention_tc_splits(n_tiles * ((H + hp - 1) // hp),
-                                                                                         int(step.max_context))
+        pairs = lib.tlc_latent_attention_tc_tile(T, B, R, r)          # (row, head) pairs a tile: 128 for prompts, else 64
+        n_tiles = T // (pairs // hp) + B
+        n_split = min(64, key_ranges) if key_ranges > 0 else lib.tlc_latent_attention_tc_splits(n_tiles * ((H + hp - 1) // hp),
+                                                                                                  int(step.max_context))
         part_o = part_ml = None
         if n_split > 1:
             part_o = torch.empty((T, H, n_split, R), dtype=torch.float32, device=qa.device)
             part_ml = torch.empty((T, H, n_split, 2), dtype=torch.float32, device=qa.device)
         _call("tlc_latent_attention_tc", qa.data_ptr(), pages.data_ptr(), sink.data_ptr(), block_table.data_ptr(),
               block_table.shape[1], step.cu_seqlens.data_ptr(), step.slots.data_ptr(), step.start_pos.data_ptr(),
-              out.data_ptr(), _p(part_o), _p(part_ml), B, T, n_tiles, H, R, r, float(scale), int(n_split), _stream())
+              out.data_ptr(), _p(part_o), _p(part_ml), B, T, pairs, n_tiles, H, R, r, float(scale), int(n_split), _stream())
         return
     _call("tlc_latent_attention", qa.data_ptr(), pages.data_ptr(), dtype_code(pages.dtype), sink.data_ptr(),
           block_table.data_ptr(), block_table.shape[1], step.positions.data_ptr(), step.row_seq.data_ptr(),
           step.slots.data_ptr(), out.data_ptr(), T, H, R, r, float(scale), _stream())
+
+
+_grouped_mma = not bool(int(os.environ.get("TLC_DISABLE_GROUPED_MMA", "0")))
+
+
+def grouped_mma(on: bool) -> None:
+    """Whether bfloat16 products per head and per expert take the mma.sync kernel where their operands are aligned for it
+    (TLC_DISABLE_GROUPED_MMA=1 sets the start value to off); for tests and comparisons."""
+    global _grouped_mma
+    _grouped_mma = bool(on)
 
 
 def linear_heads(a: torch.Tensor, a_head_stride: int, w: torch.Tensor, out: torch.Tensor, o_head_stride: int) -> None:
@@ -897,6 +912,11 @@ def linear_heads(a: torch.Tensor, a_head_stride: int, w: torch.Tensor, out: torc
     lda, ldo = _rows(a, "linear_heads input"), _rows(out, "linear_heads output")
     if (H - 1) * a_head_stride + K > max(lda, a.shape[1]) or (H - 1) * o_head_stride + N > max(ldo, out.shape[1]):
         raise KernelError("linear_heads: a head lies outside its row")
+    if _grouped_mma and library().tlc_grouped_mma_ok(dtype_code(a.dtype), dtype_code(w.dtype), a.data_ptr(), lda, int(a_head_stride),
+                                                     w.data_ptr(), K):
+        _call("tlc_linear_heads_mma", a.data_ptr(), lda, int(a_head_stride), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), ldo,
+              int(o_head_stride), T, H, N, K, _stream())
+        return
     _call("tlc_linear_heads", a.data_ptr(), dtype_code(a.dtype), lda, int(a_head_stride), w.data_ptr(), dtype_code(w.dtype),
           out.data_ptr(), dtype_code(out.dtype), ldo, int(o_head_stride), T, H, N, K, _stream())
 
@@ -958,6 +978,12 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     if not act.is_contiguous() or tuple(act.shape) != (T * top, F) or y.dtype != torch.float32 or not y.is_contiguous() \
             or y.numel() != T * top * D:
         raise KernelError("moe_experts: act [T*top, F] contiguous, y contiguous float32 [T, top, D]")
+    ldx = _rows(x, "moe input")
+    if _grouped_mma and act.dtype == torch.bfloat16 and F % 8 == 0 and D % 8 == 0 \
+            and library().tlc_grouped_mma_ok(dtype_code(x.dtype), dtype_code(w_gate_up.dtype), x.data_ptr(), ldx, 0, w_gate_up.data_ptr(), D):
+        _call("tlc_moe_experts_mma", x.data_ptr(), ldx, w_gate_up.data_ptr(), w_down.data_ptr(), order.data_ptr(), offsets.data_ptr(),
+              tile_off.data_ptr(), wts.data_ptr(), T, E, int(top), F, D, act.data_ptr(), y.data_ptr(), _stream())
+        return
     _call("tlc_moe_gate_up", x.data_ptr(), dtype_code(x.dtype), _rows(x, "moe input"), w_gate_up.data_ptr(),
           dtype_code(w_gate_up.dtype), order.data_ptr(), offsets.data_ptr(), tile_off.data_ptr(), wts.data_ptr(), T, E, int(top),
           F, D, act.data_ptr(), dtype_code(act.dtype), _stream())

@@ -75,12 +75,12 @@ class SwiGLU(Part):
 class MoEFeedForward(Part):
     """Mixture of experts with a sigmoid router.
 
-    Router scores s = sigmoid(W_router h) in 32 bits; each token takes the `top` experts with the largest scores, and
+    Router scores s = sigmoid(W_router h), the logits as 32-bit sums; each token takes the `top` experts with the largest scores, and
     its weights are those scores as they are (not renormalised).  The weight multiplies the expert's INPUT: the result
     is sum_e expert_e(s_e h), every expert a gated feed-forward W_down (silu(W_gate x) * (W_up x)) without biases.
     Gate and up are linear, so the weight is applied to their 32-bit results.  An optional shared expert (a
     feed-forward part of its own) runs on every token and is added times sigmoid(w_sg . h), one number per token; its
-    gate is computed with the router, as one more row of the router's matrix, in 32 bits.
+    gate is computed with the router, as one more row of the router's matrix.
 
     The experts' weights are stacked [E, 2F, D] and [E, D, F]; rows are sorted by expert on the device, and every
     (token, choice) pair's result gets a row of its own, which the norm that follows (or `forward`) adds in the order
@@ -111,8 +111,12 @@ class MoEFeedForward(Part):
     def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
         from .linear import matrix_dtype
         self.dtype = dtype
+        # The router's logits are 32-bit sums.  A weight stored in bfloat16 times an input rounded to bfloat16 has an exact
+        # 32-bit product, so the bfloat16 product with 32-bit accumulation IS the 32-bit result and a bfloat16 run keeps
+        # such a router in bfloat16 (the tensor cores); a router stored in 32-bit, and every 32-bit run, multiplies in 32-bit.
         rows = [tensors[self.router_name]] + ([tensors[self.shared_gate_name]] if self.shared is not None else [])
-        self.router = torch.cat([r.to(device=device, dtype=torch.float32) for r in rows], dim=0).contiguous()   # 32-bit
+        rdt = torch.bfloat16 if all(matrix_dtype(r.dtype, dtype) == torch.bfloat16 for r in rows) else torch.float32
+        self.router = torch.cat([r.to(device=device, dtype=rdt) for r in rows], dim=0).contiguous()
         names = [{k: v.format(e=e) for k, v in self.expert_names.items()} for e in range(self.E)]
         mdt = torch.bfloat16
         for n in names:

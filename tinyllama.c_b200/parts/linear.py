@@ -77,7 +77,7 @@ class StackedLinear:
                 else torch.full((s["rows"],), float(osc), dtype=torch.float64)
             scale[sl] = osc * s["in_scale"]
             if s["b"]:
-                bias[sl] = tensors[s["b"]].to(torch.float64) * osc
+                bias[sl] = tensors[s["b"]].to(device="cpu", dtype=torch.float64) * osc
                 any_bias = True
             if bool((scale[sl] != 1.0).any()):
                 any_scale = True
