@@ -298,7 +298,7 @@ def test_routing_ties_weights_and_every_experts_list():
     g = np.random.default_rng(9)
     T, E, top = 300, 7, 3
     logits = np.round(g.standard_normal((T, E + 2)) * 2.0) / 2.0                  # many exact ties
-    ids, wts, order, offsets, tile_off = ops.moe_route(dev(logits), E, top)
+    ids, wts, order, offsets, tile_off, _ = ops.moe_route(dev(logits), E, top)
     torch.cuda.synchronize()
     ids, wts, order, offsets, tile_off = (t.cpu().numpy() for t in (ids, wts, order, offsets, tile_off))
     want = np.argsort(-logits[:, :E], axis=1, kind="stable")[:, :top]
@@ -314,7 +314,7 @@ def test_routing_ties_weights_and_every_experts_list():
 @pytest.mark.parametrize("dtype,E,top,shared,D,F", [("float32", 6, 2, 20, 44, 28), ("float32", 3, 1, None, 44, 28),
                                                     ("float32", 40, 4, 12, 44, 28), ("bfloat16", 5, 5, 20, 44, 28),
                                                     ("bfloat16", 1, 1, None, 44, 28), ("bfloat16", 5, 5, 24, 48, 40),
-                                                    ("bfloat16", 3, 3, None, 136, 72)])
+                                                    ("bfloat16", 3, 3, None, 136, 72), ("bfloat16", 2, 2, 16, 64, 48)])
 def test_experts_alone(dtype, E, top, shared, D, F):
     """(Widths that are multiples of 8 in bfloat16: the tensor-core kernel; else the CUDA cores.)"""
     g = np.random.default_rng(10)
@@ -333,7 +333,7 @@ def test_experts_alone(dtype, E, top, shared, D, F):
                                                 expert_names={k: "f.e{e}." + k for k in ("gate", "up", "down")}, shared=spec,
                                                 shared_gate_name=None if shared is None else "f.shared.sg")).build()
     part.bind({k: torch.tensor(v, dtype=DT[dtype]) for k, v in W.items()}, DT[dtype], "cuda")
-    for T in (1, 3, 150):
+    for T in (1, 3, 150, 333):          # (333 rows: tiles of 64 rows where every expert gets that many)
         x = draw(g, (T, D), 1.0, dtype)
         out = torch.zeros((T, D), dtype=torch.float32, device="cuda")
         part.forward(dev(x, DT[dtype]), out, accumulate=False)

@@ -368,7 +368,7 @@ __device__ __forceinline__ float row_inv_rms(const float* xr, int D, float eps, 
 }
 
 template <typename TO>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 rmsnorm_shift_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ mu, float eps, int D,
                      const int* __restrict__ row_seq, const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                      const int* __restrict__ start_pos, float* state, TO* __restrict__ out) {
@@ -402,7 +402,8 @@ extern "C" int tlc_rmsnorm_shift(const float* x, const float* w, const float* mu
                                  const int* cu_seqlens, const int* slots, const int* start_pos, float* state, void* out,
                                  int out_dtype, cudaStream_t stream) {
   if (T == 0) return 0;
-  TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(rmsnorm_shift_kernel<TO>, dim3(T), dim3(256), 0, stream, x, w, mu, eps, D, row_seq,
+  const int nt = (T < 256 && D >= 1024) ? 1024 : 256;       // few rows: more threads a row
+  TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(rmsnorm_shift_kernel<TO>, dim3(T), dim3(nt), 0, stream, x, w, mu, eps, D, row_seq,
                                                cu_seqlens, slots, start_pos, state, (TO*)out));
   TLC_CHECK_LAUNCH("rmsnorm_shift");
   return 0;
@@ -412,7 +413,7 @@ extern "C" int tlc_rmsnorm_shift(const float* x, const float* w, const float* mu
 // y[t] = sum over p < n_parts of parts[t, p, :] (in this order) + g[t] * extra[t, :] (where extra is given), with
 // g[t] = gate[t * gate_ld], or its sigmoid;  res[t] (+)= y[t] / sqrt(mean(y[t]^2) + eps) * w, or y[t] itself where w is
 // NULL.  One block per row; the summed row waits in shared memory for its scale where it fits, else it is summed twice.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 rmsnorm_add_kernel(const float* __restrict__ parts, int n_parts, const float* __restrict__ extra,
                    const float* __restrict__ gate, int gate_ld, int gate_sigmoid, const float* __restrict__ w, float eps, int D,
                    float* __restrict__ res, int accumulate, int keep) {
@@ -432,6 +433,7 @@ rmsnorm_add_kernel(const float* __restrict__ parts, int n_parts, const float* __
     float ss = 0.f;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
       float y = 0.f;
+#pragma unroll 4
       for (int p = 0; p < n_parts; p++) y += pr[(size_t)p * D + d];
       if (er) y = fmaf(g, er[d], y);
       if (keep) yrow[d] = y;
@@ -461,7 +463,9 @@ extern "C" int tlc_rmsnorm_add(const float* parts, int n_parts, const float* ext
   if (T == 0) return 0;
   TLC_REQUIRE(n_parts >= 0 && (n_parts > 0 || extra != nullptr), "rmsnorm_add: nothing to add");
   const int keep = (size_t)D * sizeof(float) <= 40 * 1024;
-  tlc_launch(rmsnorm_add_kernel, dim3(T), dim3(256), keep ? (size_t)D * sizeof(float) : 0, stream, parts, n_parts, extra, gate, gate_ld,
+  // few rows (single-token steps): more threads a row, so that a thread's loads are few and in flight together
+  const int nt = (T < 256 && D >= 1024) ? 1024 : 256;
+  tlc_launch(rmsnorm_add_kernel, dim3(T), dim3(nt), keep ? (size_t)D * sizeof(float) : 0, stream, parts, n_parts, extra, gate, gate_ld,
              gate_sigmoid, w, eps, D, res, accumulate, keep);
   TLC_CHECK_LAUNCH("rmsnorm_add");
   return 0;

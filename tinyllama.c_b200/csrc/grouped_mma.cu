@@ -1,7 +1,8 @@
 // Grouped products on the tensor cores (mma.sync, bfloat16 operands, 32-bit sums): many small matrix products that
 // share a shape but not their weights -- one per attention head, or one per expert over the rows routed to it.
 //
-// A block computes a tile of 32 rows x 64 columns of ONE group: two warps along the rows, two along the columns.
+// A block computes a tile of 32 (or, for groups of many rows, 64) rows x 64 columns of ONE group: two warps along the
+// rows, two along the columns.
 // Operand tiles of 32 K-values arrive by cp.async (two stages) in rows padded by 16 bytes, so that ldmatrix reads
 // without bank conflicts; rows past the group's end, columns past N and K-values past K are zero-filled by the copy
 // itself.  Three uses, chosen by MODE:
@@ -41,22 +42,24 @@ struct GmArgs {
   int lda, a_hs, ldo, o_hs, T, N, K, E, top, out_f32;
 };
 
-template <int MODE>
+// WM: 16-row tiles a warp takes along the rows (1: a block's tile is 32 rows, 2: 64 rows, for groups with many rows).
+template <int MODE, int WM>
 __global__ void __launch_bounds__(128)
 grouped_mma_kernel(GmArgs p) {
   tlc_pdl(p.a, p.out, p.order, p.offsets, p.tile_off, p.wts);
   constexpr int NW = MODE == GM_GATE_UP ? 2 : 1;                   // weight tiles per stage (gate and up)
-  __shared__ __align__(16) __nv_bfloat16 As[2][GM_TM][GM_LD];
+  constexpr int TM = GM_TM * WM;
+  __shared__ __align__(16) __nv_bfloat16 As[2][TM][GM_LD];
   __shared__ __align__(16) __nv_bfloat16 Ws[2][NW][GM_TN][GM_LD];
-  __shared__ int src_row[GM_TM];
+  __shared__ int src_row[TM];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, q4 = lane & 3;
   const int wm = warp & 1, wn = warp >> 1;
   const int n0 = blockIdx.y * GM_TN;
   int group, row0, rows;
   if (MODE == GM_HEADS) {
     group = blockIdx.z;
-    row0 = blockIdx.x * GM_TM;
-    rows = min(GM_TM, p.T - row0);
+    row0 = blockIdx.x * TM;
+    rows = min(TM, p.T - row0);
   } else {
     const int tile = blockIdx.x;
     if (tile >= p.tile_off[p.E]) return;
@@ -66,19 +69,24 @@ grouped_mma_kernel(GmArgs p) {
       if (p.tile_off[mid] <= tile) lo = mid; else hi = mid - 1;
     }
     group = lo;
-    row0 = p.offsets[lo] + (tile - p.tile_off[lo]) * GM_TM;
-    rows = min(GM_TM, p.offsets[lo + 1] - row0);
-    if (tid < GM_TM) src_row[tid] = tid < rows ? p.order[row0 + tid] : 0;
+    row0 = p.offsets[lo] + (tile - p.tile_off[lo]) * TM;
+    rows = min(TM, p.offsets[lo + 1] - row0);
+    if (tid < TM) src_row[tid] = tid < rows ? p.order[row0 + tid] : 0;
     __syncthreads();
   }
   const int K = p.K, N = p.N;
-  // this thread's copies: one 16-byte piece of the A tile, two of every weight tile
-  const int ar = tid >> 2, ac = (tid & 3) * 8;
-  const __nv_bfloat16* a_src;
-  if (MODE == GM_HEADS) a_src = p.a + (size_t)group * p.a_hs + (size_t)min(row0 + ar, p.T - 1) * p.lda;
-  else if (MODE == GM_GATE_UP) a_src = p.a + (size_t)(src_row[ar] / p.top) * p.lda;
-  else a_src = p.a + (size_t)(row0 + min(ar, rows - 1)) * K;
-  const bool a_ok = ar < rows;
+  // this thread's copies: WM 16-byte pieces of the A tile, two of every weight tile
+  const int ac = (tid & 3) * 8;
+  const __nv_bfloat16* a_src[WM];
+  bool a_ok[WM];
+#pragma unroll
+  for (int j = 0; j < WM; j++) {
+    const int ar = (tid >> 2) + j * 32;
+    if (MODE == GM_HEADS) a_src[j] = p.a + (size_t)group * p.a_hs + (size_t)min(row0 + ar, p.T - 1) * p.lda;
+    else if (MODE == GM_GATE_UP) a_src[j] = p.a + (size_t)(src_row[ar] / p.top) * p.lda;
+    else a_src[j] = p.a + (size_t)(row0 + min(ar, rows - 1)) * K;
+    a_ok[j] = ar < rows;
+  }
   const __nv_bfloat16* wg = p.w + (size_t)group * (MODE == GM_GATE_UP ? 2 : 1) * N * K;
   const __nv_bfloat16* w_src[NW][2];
   bool w_ok[2];
@@ -95,7 +103,9 @@ grouped_mma_kernel(GmArgs p) {
     const int k = k0 + ac;
     const bool k_ok = k < K;
     const int kk = k_ok ? k : 0;
-    gm_cp16(as_u + (uint32_t)((buf * GM_TM + ar) * GM_LD + ac) * 2, a_src + kk, (a_ok && k_ok) ? 16 : 0);
+#pragma unroll
+    for (int j = 0; j < WM; j++)
+      gm_cp16(as_u + (uint32_t)((buf * TM + (tid >> 2) + j * 32) * GM_LD + ac) * 2, a_src[j] + kk, (a_ok[j] && k_ok) ? 16 : 0);
 #pragma unroll
     for (int u = 0; u < NW; u++)
 #pragma unroll
@@ -103,13 +113,15 @@ grouped_mma_kernel(GmArgs p) {
         gm_cp16(ws_u + (uint32_t)(((buf * NW + u) * GM_TN + (tid >> 2) + j * 32) * GM_LD + ac) * 2, w_src[u][j] + kk,
                 (w_ok[j] && k_ok) ? 16 : 0);
   };
-  float acc[NW][4][4];
+  float acc[NW][WM][4][4];
 #pragma unroll
   for (int u = 0; u < NW; u++)
 #pragma unroll
-    for (int j = 0; j < 4; j++)
+    for (int i = 0; i < WM; i++)
 #pragma unroll
-      for (int e = 0; e < 4; e++) acc[u][j][e] = 0.f;
+      for (int j = 0; j < 4; j++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) acc[u][i][j][e] = 0.f;
   const int n_k = (K + GM_TK - 1) / GM_TK;
   load(0, 0);
   gm_commit();
@@ -121,49 +133,57 @@ grouped_mma_kernel(GmArgs p) {
     __syncthreads();
 #pragma unroll
     for (int k16 = 0; k16 < GM_TK; k16 += 16) {
-      uint32_t a0, a1, a2, a3;
-      gm_ldsm4(a0, a1, a2, a3, as_u + (uint32_t)((buf * GM_TM + wm * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * GM_LD + k16 + (lane >> 4) * 8) * 2);
+      uint32_t af[WM][4];
+#pragma unroll
+      for (int i = 0; i < WM; i++)
+        gm_ldsm4(af[i][0], af[i][1], af[i][2], af[i][3],
+                 as_u + (uint32_t)((buf * TM + (wm * WM + i) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * GM_LD + k16 + (lane >> 4) * 8) * 2);
 #pragma unroll
       for (int u = 0; u < NW; u++)
 #pragma unroll
         for (int jp = 0; jp < 2; jp++) {
           uint32_t b0, b1, b2, b3;
           gm_ldsm4(b0, b1, b2, b3, ws_u + (uint32_t)(((buf * NW + u) * GM_TN + wn * 32 + jp * 16 + (lane & 7) + (lane >> 4) * 8) * GM_LD + k16 + ((lane >> 3) & 1) * 8) * 2);
-          gm_mma(acc[u][2 * jp], a0, a1, a2, a3, b0, b1);
-          gm_mma(acc[u][2 * jp + 1], a0, a1, a2, a3, b2, b3);
+#pragma unroll
+          for (int i = 0; i < WM; i++) {
+            gm_mma(acc[u][i][2 * jp], af[i][0], af[i][1], af[i][2], af[i][3], b0, b1);
+            gm_mma(acc[u][i][2 * jp + 1], af[i][0], af[i][1], af[i][2], af[i][3], b2, b3);
+          }
         }
     }
     __syncthreads();
   }
   gm_wait<0>();
-  // epilogue: this thread holds rows (wm*16 + g, + 8) and columns wn*32 + 8j + 2q, +1
+  // epilogue: this thread holds rows ((wm*WM + i)*16 + g, + 8) and columns wn*32 + 8j + 2q, +1
 #pragma unroll
-  for (int e = 0; e < 2; e++) {
-    const int rl = wm * 16 + g + e * 8;
-    if (rl >= rows) continue;
-    float wgt = 1.0f;
-    size_t orow;
-    if (MODE == GM_HEADS) orow = (size_t)group * p.o_hs + (size_t)(row0 + rl) * p.ldo;
-    else if (MODE == GM_GATE_UP) { orow = (size_t)(row0 + rl) * N; wgt = p.wts[src_row[rl]]; }
-    else orow = (size_t)src_row[rl] * N;
+  for (int i = 0; i < WM; i++)
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
+    for (int e = 0; e < 2; e++) {
+      const int rl = (wm * WM + i) * 16 + g + e * 8;
+      if (rl >= rows) continue;
+      float wgt = 1.0f;
+      size_t orow;
+      if (MODE == GM_HEADS) orow = (size_t)group * p.o_hs + (size_t)(row0 + rl) * p.ldo;
+      else if (MODE == GM_GATE_UP) { orow = (size_t)(row0 + rl) * N; wgt = p.wts[src_row[rl]]; }
+      else orow = (size_t)src_row[rl] * N;
 #pragma unroll
-      for (int c = 0; c < 2; c++) {
-        const int n = n0 + wn * 32 + 8 * j + 2 * q4 + c;
-        if (n >= N) continue;
-        const float v = acc[0][j][2 * e + c];
-        if (MODE == GM_GATE_UP) {
-          const float u = acc[NW - 1][j][2 * e + c];
-          reinterpret_cast<__nv_bfloat16*>(p.out)[orow + n] = __float2bfloat16_rn(silu_quick(wgt * v) * (wgt * u));
-        } else if (MODE == GM_DOWN || p.out_f32) {
-          reinterpret_cast<float*>(p.out)[orow + n] = v;
-        } else {
-          reinterpret_cast<__nv_bfloat16*>(p.out)[orow + n] = __float2bfloat16_rn(v);
+      for (int j = 0; j < 4; j++) {
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+          const int n = n0 + wn * 32 + 8 * j + 2 * q4 + c;
+          if (n >= N) continue;
+          const float v = acc[0][i][j][2 * e + c];
+          if (MODE == GM_GATE_UP) {
+            const float u = acc[NW - 1][i][j][2 * e + c];
+            reinterpret_cast<__nv_bfloat16*>(p.out)[orow + n] = __float2bfloat16_rn(silu_quick(wgt * v) * (wgt * u));
+          } else if (MODE == GM_DOWN || p.out_f32) {
+            reinterpret_cast<float*>(p.out)[orow + n] = v;
+          } else {
+            reinterpret_cast<__nv_bfloat16*>(p.out)[orow + n] = __float2bfloat16_rn(v);
+          }
         }
       }
     }
-  }
 }
 
 static inline bool gm_aligned(const void* p, long long ld_elems) { return ((uintptr_t)p % 16) == 0 && ld_elems % 8 == 0; }
@@ -180,8 +200,11 @@ extern "C" int tlc_linear_heads_mma(const void* a, int lda, int a_hs, const void
   GmArgs p = {};
   p.a = (const __nv_bfloat16*)a; p.w = (const __nv_bfloat16*)w; p.out = out;
   p.lda = lda; p.a_hs = a_hs; p.ldo = ldo; p.o_hs = o_hs; p.T = T; p.N = N; p.K = K; p.out_f32 = out_dtype == TLC_F32;
-  dim3 grid((T + GM_TM - 1) / GM_TM, (N + GM_TN - 1) / GM_TN, H);
-  tlc_launch(grouped_mma_kernel<GM_HEADS>, grid, dim3(128), 0, stream, p);
+  if (T >= 512) {                                           // many rows: 64-row tiles
+    tlc_launch(grouped_mma_kernel<GM_HEADS, 2>, dim3((T + 63) / 64, (N + GM_TN - 1) / GM_TN, H), dim3(128), 0, stream, p);
+  } else {
+    tlc_launch(grouped_mma_kernel<GM_HEADS, 1>, dim3((T + GM_TM - 1) / GM_TM, (N + GM_TN - 1) / GM_TN, H), dim3(128), 0, stream, p);
+  }
   TLC_CHECK_LAUNCH("linear_heads_mma");
   return 0;
 }
@@ -190,19 +213,22 @@ extern "C" int tlc_linear_heads_mma(const void* a, int lda, int a_hs, const void
 // [T*top, F] bfloat16 scratch, y [T*top, D] float.
 extern "C" int tlc_moe_experts_mma(const void* x, int ldx, const void* wgu, const void* wd, const int* order, const int* offsets,
                                    const int* tile_off, const float* wts, int T, int E, int top, int F, int D, void* act, float* y,
-                                   cudaStream_t stream) {
+                                   int tile_rows, cudaStream_t stream) {
   if (T == 0) return 0;
+  TLC_REQUIRE(tile_rows == 32 || tile_rows == 64, "moe_experts_mma: tiles of %d rows are not built (32 or 64, as the routing was made)", tile_rows);
   TLC_REQUIRE(D % 8 == 0 && F % 8 == 0 && gm_aligned(x, ldx) && gm_aligned(wgu, D) && gm_aligned(wd, F) && gm_aligned(act, F),
               "moe_experts_mma: operands are not aligned for 16-byte copies");
   const long long pairs = (long long)T * top;
-  const int tiles = (int)(pairs / GM_TM + (pairs < E ? pairs : E));
+  const int tiles = (int)(pairs / tile_rows + (pairs < E ? pairs : E));
   GmArgs p = {};
   p.order = order; p.offsets = offsets; p.tile_off = tile_off; p.wts = wts; p.E = E; p.top = top; p.T = T;
   p.a = (const __nv_bfloat16*)x; p.lda = ldx; p.w = (const __nv_bfloat16*)wgu; p.out = act; p.N = F; p.K = D;
-  tlc_launch(grouped_mma_kernel<GM_GATE_UP>, dim3(tiles, (F + GM_TN - 1) / GM_TN), dim3(128), 0, stream, p);
+  if (tile_rows == 64) tlc_launch(grouped_mma_kernel<GM_GATE_UP, 2>, dim3(tiles, (F + GM_TN - 1) / GM_TN), dim3(128), 0, stream, p);
+  else tlc_launch(grouped_mma_kernel<GM_GATE_UP, 1>, dim3(tiles, (F + GM_TN - 1) / GM_TN), dim3(128), 0, stream, p);
   TLC_CHECK_LAUNCH("moe_gate_up_mma");
   p.a = (const __nv_bfloat16*)act; p.lda = F; p.w = (const __nv_bfloat16*)wd; p.out = y; p.N = D; p.K = F;
-  tlc_launch(grouped_mma_kernel<GM_DOWN>, dim3(tiles, (D + GM_TN - 1) / GM_TN), dim3(128), 0, stream, p);
+  if (tile_rows == 64) tlc_launch(grouped_mma_kernel<GM_DOWN, 2>, dim3(tiles, (D + GM_TN - 1) / GM_TN), dim3(128), 0, stream, p);
+  else tlc_launch(grouped_mma_kernel<GM_DOWN, 1>, dim3(tiles, (D + GM_TN - 1) / GM_TN), dim3(128), 0, stream, p);
   TLC_CHECK_LAUNCH("moe_down_mma");
   return 0;
 }

@@ -20,7 +20,7 @@
 // dkv_off < 0 for a layer that reads another layer's rows.  Writes qn [T, H*dn] (the unrotated query parts), the
 // rotated parts into the last r columns of every head of qa [T, H*(R+r)], and, with a down-projection, the cache row.
 template <typename TC>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 latent_prepare_kernel(const float* __restrict__ proj, int ld, int q_off, int dkv_off, const float* __restrict__ cw, float eps,
                       const float* __restrict__ inv_freq, int rot, const int* __restrict__ positions,
                       const int* __restrict__ row_seq, const int* __restrict__ slots, const int* __restrict__ block_table,
@@ -84,7 +84,8 @@ extern "C" int tlc_latent_prepare(const float* proj, int ld, int q_off, int dkv_
                                   int dn, int r, int R, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= r, "latent_prepare: %d rotated dimensions of %d", rot, r);
-  TLC_DISPATCH_DTYPE(dtype, TC, tlc_launch(latent_prepare_kernel<TC>, dim3(T), dim3(128), 0, stream, proj, ld, q_off, dkv_off, cw, eps,
+  const int nt = T < 256 ? 512 : 128;                       // few rows: more threads a row
+  TLC_DISPATCH_DTYPE(dtype, TC, tlc_launch(latent_prepare_kernel<TC>, dim3(T), dim3(nt), 0, stream, proj, ld, q_off, dkv_off, cw, eps,
                                            inv_freq, rot, positions, row_seq, slots, block_table, max_pages, (TC*)pages, (TC*)qn,
                                            (TC*)qa, H, dn, r, R));
   TLC_CHECK_LAUNCH("latent_prepare");

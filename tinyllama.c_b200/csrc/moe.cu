@@ -17,27 +17,37 @@
 
 #define MOE_TM 32
 
-// A thread per token: its `top` experts by descending logit (lowest index first on ties) and their weights.
+// A warp per token: its `top` experts by descending logit (lowest index first on ties) and their weights.  Every round a
+// lane finds the best of its experts (lane, lane + 32, ...) that come after the last choice in that order, and the
+// warp the best of the lanes.
 __global__ void __launch_bounds__(128)
 moe_topk_kernel(const float* __restrict__ logits, int ld, int T, int E, int top, int* __restrict__ ids, float* __restrict__ wts) {
   tlc_pdl(logits, ids, wts);
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= T) return;
   const float* lr = logits + (size_t)t * ld;
   float last = INFINITY;
   int last_e = -1;
   for (int k = 0; k < top; k++) {
-    // the largest logit below (last, last_e) in the order (value descending, index ascending)
     float best = -INFINITY;
-    int be = -1;
-    for (int e = 0; e < E; e++) {
+    int be = 0x7fffffff;                     // none yet
+    for (int e = lane; e < E; e += 32) {
       const float v = lr[e];
       const bool after = v < last || (v == last && e > last_e);
-      if (after && (be < 0 || v > best)) { best = v; be = e; }
+      if (after && (be == 0x7fffffff || v > best)) { best = v; be = e; }   // (a lane's experts come in ascending order)
     }
-    if (be < 0) be = 0;                      // (NaN logits: no order; keep indices valid)
-    ids[t * top + k] = be;
-    wts[t * top + k] = 1.0f / (1.0f + expf(-lr[be]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      const bool take = oe != 0x7fffffff && (be == 0x7fffffff || ov > best || (ov == best && oe < be));
+      if (take) { best = ov; be = oe; }
+    }
+    if (be == 0x7fffffff) be = 0;            // (NaN logits: no order; keep indices valid)
+    if (lane == 0) {
+      ids[t * top + k] = be;
+      wts[t * top + k] = 1.0f / (1.0f + expf(-lr[be]));
+    }
     last = lr[be];
     last_e = be;
   }
@@ -73,12 +83,13 @@ moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int E, int tm, int* __
 }
 
 extern "C" int tlc_moe_route(const float* logits, int ld, int T, int E, int top, int* ids, float* wts, int* order, int* offsets,
-                             int* tile_off, cudaStream_t stream) {
+                             int* tile_off, int tile_rows, cudaStream_t stream) {
   if (T == 0) return 0;
+  TLC_REQUIRE(tile_rows >= 1, "moe_route: tiles of %d rows", tile_rows);
   TLC_REQUIRE(E >= 1 && top >= 1 && top <= E && E <= 4096, "moe_route: %d experts, %d chosen", E, top);
-  tlc_launch(moe_topk_kernel, dim3((T + 127) / 128), dim3(128), 0, stream, logits, ld, T, E, top, ids, wts);
+  tlc_launch(moe_topk_kernel, dim3((T + 3) / 4), dim3(128), 0, stream, logits, ld, T, E, top, ids, wts);
   TLC_CHECK_LAUNCH("moe_topk");
-  tlc_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), stream, (const int*)ids, T * top, E, MOE_TM, order,
+  tlc_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), stream, (const int*)ids, T * top, E, tile_rows, order,
              offsets, tile_off);
   TLC_CHECK_LAUNCH("moe_sort");
   return 0;

@@ -271,9 +271,10 @@ int tlc_mingru_scan(const float* proj, int ld, int z_off, int u_off, int g_off, 
 /* ---- mixture of experts (moe.cu) ------------------------------------------------------------------------
  * tlc_moe_route: logits float [T, ld] (E columns) -> per token its `top` experts by descending logit (lowest index
  * first on ties) in ids [T*top] with weights wts = sigmoid(logit); order [T*top] lists the pairs (t * top + k) sorted
- * by expert, offsets [E+1] every expert's first sorted position, tile_off [E+1] its first tile of 32 sorted rows. */
+ * by expert, offsets [E+1] every expert's first sorted position, tile_off [E+1] its first tile of tile_rows sorted rows
+ * (32 for tlc_moe_gate_up / tlc_moe_down; 32 or 64 for tlc_moe_experts_mma, which is told the same number). */
 int tlc_moe_route(const float* logits, int ld, int T, int E, int top, int* ids, float* wts, int* order, int* offsets,
-                  int* tile_off, cudaStream_t stream);
+                  int* tile_off, int tile_rows, cudaStream_t stream);
 /* act[i, :F] = silu(w g) * (w u) for sorted position i: g | u = wgu[e] x[token], wgu [E, 2F, D], w the pair's weight. */
 int tlc_moe_gate_up(const void* x, int x_dtype, int ldx, const void* wgu, int w_dtype, const int* order,
                     const int* offsets, const int* tile_off, const float* wts, int T, int E, int top, int F, int D,
@@ -291,7 +292,7 @@ int tlc_linear_heads_mma(const void* a, int lda, int a_hs, const void* w, void* 
                          int T, int H, int N, int K, cudaStream_t stream);
 int tlc_moe_experts_mma(const void* x, int ldx, const void* wgu, const void* wd, const int* order, const int* offsets,
                         const int* tile_off, const float* wts, int T, int E, int top, int F, int D, void* act, float* y,
-                        cudaStream_t stream);
+                        int tile_rows, cudaStream_t stream);
 
 /* ---- sampling (sampling.cu) ------------------------------------------------------------------------ */
 /* out[r] = first index of the maximum of logits[r].  work: NULL (one block a row), or 12 * R bytes, 8-byte

@@ -104,9 +104,9 @@ _SIGNATURES = {
     "tlc_linear_heads": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "tlc_grouped_mma_ok": (_i, [_i, _i, _vp, _i, _i, _vp, _i]),
     "tlc_linear_heads_mma": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
-    "tlc_moe_experts_mma": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "tlc_moe_experts_mma": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp]),
     "tlc_mingru_scan": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _vp, _vp]),
-    "tlc_moe_route": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "tlc_moe_route": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "tlc_moe_gate_up": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp]),
     "tlc_moe_down": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
     "tlc_argmax": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
@@ -944,10 +944,24 @@ def mingru_scan(proj: torch.Tensor, z_off: int, u_off: int, g_off: int, width: i
 
 
 # ---- mixture of experts ------------------------------------------------------------------------------------
-def moe_route(logits: torch.Tensor, n_experts: int, top: int):
+def _moe_mma_ok(x: torch.Tensor, w_gate_up: torch.Tensor, act_dtype: torch.dtype) -> bool:
+    D, F = w_gate_up.shape[2], w_gate_up.shape[1] // 2
+    return bool(_grouped_mma and act_dtype == torch.bfloat16 and F % 8 == 0 and D % 8 == 0
+                and library().tlc_grouped_mma_ok(dtype_code(x.dtype), dtype_code(w_gate_up.dtype), x.data_ptr(), _rows(x, "moe input"),
+                                                 0, w_gate_up.data_ptr(), D))
+
+
+def moe_tile_rows(x: torch.Tensor, w_gate_up: torch.Tensor, act_dtype: torch.dtype, top: int) -> int:
+    """Rows of a tile of the experts' products for this input: 64 where the tensor-core kernel runs and an expert gets
+    64 rows or more on average, else 32.  The routing is made for that number (moe_route) and carries it."""
+    E = w_gate_up.shape[0]
+    return 64 if _moe_mma_ok(x, w_gate_up, act_dtype) and x.shape[0] * top >= 64 * E else 32
+
+
+def moe_route(logits: torch.Tensor, n_experts: int, top: int, tile_rows: int = 32):
     """Routing of every row of logits (float32 [T, >= E], the first E columns): returns (ids [T*top] int32, weights
-    [T*top] float32 = sigmoid of the chosen logits, order [T*top], offsets [E+1], tile_off [E+1]) as tlc_moe_route
-    describes them."""
+    [T*top] float32 = sigmoid of the chosen logits, order [T*top], offsets [E+1], tile_off [E+1], tile_rows) as
+    tlc_moe_route describes them."""
     _gpu(logits)
     T = logits.shape[0]
     if logits.dtype != torch.float32 or logits.shape[1] < n_experts:
@@ -958,9 +972,11 @@ def moe_route(logits: torch.Tensor, n_experts: int, top: int):
     offsets = ints[2 * T * top:2 * T * top + n_experts + 1]
     tile_off = ints[2 * T * top + n_experts + 1:]
     wts = torch.empty(T * top, dtype=torch.float32, device=dev)
+    global _launches
+    _launches += 1                      # (two kernels)
     _call("tlc_moe_route", logits.data_ptr(), _rows(logits, "router logits"), T, int(n_experts), int(top), ids.data_ptr(),
-          wts.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_off.data_ptr(), _stream())
-    return ids, wts, order, offsets, tile_off
+          wts.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_off.data_ptr(), int(tile_rows), _stream())
+    return ids, wts, order, offsets, tile_off, int(tile_rows)
 
 
 def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, routing, top: int, act: torch.Tensor,
@@ -968,7 +984,7 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     """y[t, k, :] = expert_k(weight * x[t]) for every chosen (token, expert) pair: w_gate_up [E, 2F, D], w_down
     [E, D, F]; act [T*top, F] is scratch of the activation type, y float32 [T, top, D]."""
     _gpu(x, w_gate_up, w_down, act, y)
-    ids, wts, order, offsets, tile_off = routing
+    ids, wts, order, offsets, tile_off, tile_rows = routing
     T, D = x.shape
     E, F2, _ = w_gate_up.shape
     F = F2 // 2
@@ -979,11 +995,12 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
             or y.numel() != T * top * D:
         raise KernelError("moe_experts: act [T*top, F] contiguous, y contiguous float32 [T, top, D]")
     ldx = _rows(x, "moe input")
-    if _grouped_mma and act.dtype == torch.bfloat16 and F % 8 == 0 and D % 8 == 0 \
-            and library().tlc_grouped_mma_ok(dtype_code(x.dtype), dtype_code(w_gate_up.dtype), x.data_ptr(), ldx, 0, w_gate_up.data_ptr(), D):
+    if _moe_mma_ok(x, w_gate_up, act.dtype):
         _call("tlc_moe_experts_mma", x.data_ptr(), ldx, w_gate_up.data_ptr(), w_down.data_ptr(), order.data_ptr(), offsets.data_ptr(),
-              tile_off.data_ptr(), wts.data_ptr(), T, E, int(top), F, D, act.data_ptr(), y.data_ptr(), _stream())
+              tile_off.data_ptr(), wts.data_ptr(), T, E, int(top), F, D, act.data_ptr(), y.data_ptr(), tile_rows, _stream())
         return
+    if tile_rows != 32:
+        raise KernelError("moe_experts: the CUDA-core products take a routing made for tiles of 32 rows")
     _call("tlc_moe_gate_up", x.data_ptr(), dtype_code(x.dtype), _rows(x, "moe input"), w_gate_up.data_ptr(),
           dtype_code(w_gate_up.dtype), order.data_ptr(), offsets.data_ptr(), tile_off.data_ptr(), wts.data_ptr(), T, E, int(top),
           F, D, act.data_ptr(), dtype_code(act.dtype), _stream())

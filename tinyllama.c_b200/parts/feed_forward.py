@@ -136,7 +136,7 @@ class MoEFeedForward(Part):
         n_logits = self.router.shape[0]
         logits = scratch_buf("moe.logits", (T, n_logits), torch.float32, dev)
         ops.linear(normed, self.router, logits)
-        routing = ops.moe_route(logits, self.E, self.top)
+        routing = ops.moe_route(logits, self.E, self.top, ops.moe_tile_rows(normed, self.w_gate_up, self.dtype, self.top))
         act = scratch_buf("moe.act", (T * self.top, self.F), self.dtype, dev)
         parts = scratch_buf("moe.parts", (T, self.top, self.hidden), torch.float32, dev)
         ops.moe_experts(normed, self.w_gate_up, self.w_down, routing, self.top, act, parts)
