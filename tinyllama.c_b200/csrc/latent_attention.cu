@@ -265,7 +265,7 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bflo
                            const float* __restrict__ sink, const int* __restrict__ block_table, int max_pages,
                            const int* __restrict__ cu_seqlens, const int* __restrict__ slots, const int* __restrict__ start_pos,
                            __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int B, int H,
-                           int HP, int R, int r, float scale, int n_split) {
+                           int HP, int R, int r, float scale, int n_split, int n_tiles) {
   tlc_pdl(qa, pages, out, part_o, part_ml);
   constexpr int LTM = NWARP * 16, NT = NWARP * 32;
   extern __shared__ __align__(16) unsigned char lt_smem[];
@@ -275,8 +275,11 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bflo
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, q4 = lane & 3;
   const int rpt = LTM / HP, n_hg = (H + HP - 1) / HP;    // rows per tile, head groups
   // which sequence, rows and heads this tile covers
+  // the last rows of a sequence see the most keys: the grid starts with the highest tiles, so that the longest blocks
+  // run first and the short ones fill the tail
   int tile = blockIdx.x / n_hg;
   const int hg = blockIdx.x - tile * n_hg;
+  tile = n_tiles - 1 - tile;
   int b = 0, first = 0, len = 0;
   for (; b < B; b++) {
     first = cu_seqlens[b];
@@ -534,7 +537,7 @@ extern "C" int tlc_latent_attention_tc(const void* qa, const void* pages, const 
   typedef const __nv_bfloat16* BP;
 #define LT_LAUNCH(NV, NW)                                                                                                      \
   tlc_launch(latent_attention_tc_kernel<NV, NW>, grid, dim3(NW * 32), smem, stream, (BP)qa, (BP)pages, sink, block_table, max_pages, \
-             cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, part_o, part_ml, B, H, HP, R, r, scale, n_split)
+             cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, part_o, part_ml, B, H, HP, R, r, scale, n_split, n_tiles)
   if (tile_pairs == 128) { if (R <= 128) LT_LAUNCH(8, 8); else LT_LAUNCH(16, 8); }
   else { if (R <= 128) LT_LAUNCH(8, 4); else LT_LAUNCH(16, 4); }
 #undef LT_LAUNCH

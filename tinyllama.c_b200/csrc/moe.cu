@@ -17,7 +17,7 @@
 
 #define MOE_TM 32
 
-// A warp per token: its `top` experts by descending logit (lowest index first on ties) and their weights.  Every round a
+// A warp per token: its `top` experts by descending logit (lowest index first on ties) and their weights.  In every pass a
 // lane finds the best of its experts (lane, lane + 32, ...) that come after the last choice in that order, and the
 // warp the best of the lanes.
 __global__ void __launch_bounds__(128)
