@@ -248,8 +248,9 @@ def _attend(qa, rows, sink, scale, positions, H, R, r, dtype, tc, key_ranges=0):
     return out.float().cpu().numpy().reshape(T, H, R)
 
 
+@pytest.mark.parametrize("sizes", [(3, 32, 16), (70, 16, 16), (2, 160, 32)])
 @pytest.mark.parametrize("kernel", ["warp32", "warp16", "tc", "tc3", "tc5"])
-def test_one_key_decides_far_back_at_page_borders_own_position_and_beyond(kernel):
+def test_one_key_decides_far_back_at_page_borders_own_position_and_beyond(kernel, sizes):
     """300 cached rows of small random values; one of them, `hot`, lines up with head 1's query and scores far above the
     rest, so the output of head 1 is that row's latent wherever the key is visible and the plain average where it is
     not: keys at position 0, at both sides of the page borders, far back, at the query's own position and one beyond it
@@ -258,16 +259,16 @@ def test_one_key_decides_far_back_at_page_borders_own_position_and_beyond(kernel
     dtype = "float32" if kernel == "warp32" else "bfloat16"
     tc, ranges = kernel.startswith("tc"), int(kernel[2:] or 1) if kernel.startswith("tc") else 0
     g = np.random.default_rng(7)
-    H, R, r, scale = 3, 32, 16, 0.5
+    (H, R, r), scale = sizes, 0.5          # (70 heads: two groups of 64 a row; a latent of 160: the wider accumulator)
     n = 300
-    for hot in (0, 63, 64, 127, 128, 255, 256, 290, 299):
+    for hot in ((0, 63, 64, 127, 128, 255, 256, 290, 299) if H == 3 else (0, 64, 127, 299)):
         rows = draw(g, (n, R + r), 0.1, dtype)
         rows[hot] = draw(g, (R + r,), 1.0, dtype)
-        sink = np.array([0.0, -1.0, 0.5])
+        sink = np.resize(np.array([0.0, -1.0, 0.5]), H)
         for positions in (list(range(284, 300)), [hot], [max(hot - 1, 0)], [299]):
             T = len(positions)
             qa = draw(g, (T, H, R + r), 0.1, dtype)
-            qa[:, 1] = plain.bf16_round(rows[hot] * 6.0) if dtype == "bfloat16" else rows[hot] * 6.0
+            qa[:, 1] = plain.bf16_round(rows[hot] * 6.0 * 48.0 / (R + r)) if dtype == "bfloat16" else rows[hot] * 6.0 * 48.0 / (R + r)
             got = _attend(qa, rows, sink, scale, positions, H, R, r, dtype, tc, ranges)
             for i, p in enumerate(positions):
                 want = plain.attend_latent(qa[i], rows, sink, scale, p + 1)[:, :R]
