@@ -109,7 +109,7 @@ def latent_attention(h, W, p, m, positions, c, kr, rnd=_same):
 
 
 def mingru(h, W, p, state=None, rnd=_same):
-    """Gated recurrence whose gates read only the current token; returns (output, last state)."""
+    """Recurrence whose gate and candidate are computed from the input rows alone; returns (output, last state)."""
     z = sigmoid(rnd(h) @ rnd(W[p + "z"]).T + W[p + "z.b"])
     u = rnd(h) @ rnd(W[p + "x"]).T + W[p + "x.b"]
     cand = np.where(u >= 0, u + 0.5, sigmoid(u))
@@ -132,7 +132,7 @@ def dense_ff(h, W, p, rnd=_same):
 
 
 def route(h, W, p, top):
-    """Scores of every expert and, per row, the `top` experts with the largest ones (lowest index first on ties)."""
+    """Scores of every expert and, per row, its `top` highest-scoring experts (lowest index first on ties)."""
     s = sigmoid(h @ W[p + "router"].T)
     order = np.argsort(-s, axis=-1, kind="stable")[:, :top]
     return s, order

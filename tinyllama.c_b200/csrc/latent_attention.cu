@@ -9,8 +9,8 @@
 // afterwards (tlc_linear_heads again).  So the cache is read once for all heads, and a layer that borrows another
 // layer's latents needs nothing but its own U and V.
 //
-// The softmax has a sink: a learned logit per head that takes part in the maximum and the denominator only (it is not
-// scaled, has no value, and counts once).  Scores, softmax statistics, rotation angles, the norm of c and all
+// The softmax has a sink: a per-head logit, used as stored (the score scale does not apply to it), that adds a single
+// term to the denominator and nothing to the weighted sum of values.  Scores, softmax statistics, rotation angles, the norm of c and all
 // accumulators are 32-bit.  The rotation is the interleaved one: dimensions (2i, 2i+1) of the first `rot` dimensions
 // turn by position * inv_freq[i]; what lies beyond passes unchanged.
 #include "common.cuh"

@@ -6,7 +6,7 @@
 // each expert's rows form one contiguous range of a permutation; nothing goes through the host, so the same launches
 // serve any routing (and a captured graph).
 //
-// Experts (tlc_moe_gate_up, tlc_moe_down): the weight multiplies the expert's INPUT, expert(w h); gate and up are
+// Experts (tlc_moe_gate_up, tlc_moe_down): an expert is fed the token scaled by its weight, expert(w h); gate and up are
 // linear, so W (w h) = w (W h) and the epilogue of the first product applies w in 32 bits: act(w g) * (w u).  The
 // second product writes every pair's result into its own row of [T, top, D]; the norm that follows adds a token's rows
 // in the order of its choices, so the sum does not depend on where other tokens went.

@@ -1,4 +1,4 @@
-// minGRU: a gated recurrence whose gates read only the current token.
+// minGRU: a recurrence whose update gate and candidate depend on the token's input alone, never on the previous state.
 //
 // Per channel, with the projections zr, ur, gr of the token (biases already added):
 //   z = sigmoid(zr);  cand = ur + 1/2 where ur >= 0, sigmoid(ur) where ur < 0;  S <- (1 - z) S + z cand;

@@ -1,5 +1,5 @@
 """Turevik: per layer a latent-attention or minGRU mixer and a dense or mixture-of-experts feed-forward, each sublayer
-between two norms, with a token shift on what the mixer reads.
+between two norms, with a token shift applied to the mixer's input.
 
     x <- x + norm1b(mixer(shift(norm1(x))))        x <- x + norm2b(ff(norm2(x)))
 

@@ -75,8 +75,8 @@ class SwiGLU(Part):
 class MoEFeedForward(Part):
     """Mixture of experts with a sigmoid router.
 
-    Router scores s = sigmoid(W_router h), the logits as 32-bit sums; each token takes the `top` experts with the largest scores, and
-    its weights are those scores as they are (not renormalised).  The weight multiplies the expert's INPUT: the result
+    Router scores s = sigmoid(W_router h), the logits as 32-bit sums; a token is routed to its `top` highest-scoring experts, and
+    its weights are those scores unchanged (they need not sum to one).  An expert is fed the token scaled by its weight: the result
     is sum_e expert_e(s_e h), every expert a gated feed-forward W_down (silu(W_gate x) * (W_up x)) without biases.
     Gate and up are linear, so the weight is applied to their 32-bit results.  An optional shared expert (a
     feed-forward part of its own) runs on every token and is added times sigmoid(w_sg . h), one number per token; its

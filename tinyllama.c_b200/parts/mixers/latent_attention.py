@@ -4,7 +4,8 @@ A token's input h is projected down to R + r values: the first R, RMS-normed wit
 latent c; the last r, rotated, are a key part kr that every head shares.  Only [c | kr] is cached.
 Head i has up-projections of its own: key_i = U_i c (dn values) and value_i = V_i c (dv values); its query
 is (qn_i | qr_i) with qr_i rotated like kr; score = (qn_i . key_i + qr_i . kr) * scale; the softmax's
-denominator also holds exp(sink_i), a learned number per head with no key and no value.
+denominator gets one extra term exp(sink_i): sink_i is a per-head parameter, a logit that attracts probability mass
+without contributing any value vector.
 
 The keys are never built: qn_i . U_i c = (U_i^T qn_i) . c, so the query is carried into the latent space
 (one product per head), every head attends over the same cached rows with the query [U_i^T qn_i | qr_i]

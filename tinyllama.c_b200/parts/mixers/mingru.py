@@ -1,4 +1,5 @@
-"""minGRU mixer: a gated recurrence whose gates read only the current token.
+"""minGRU mixer: a recurrence over tokens whose update gate and candidate are functions of the token's input alone
+(never of the previous state).
 
 z = sigmoid(W_z h + b_z), u = W_x h + b_x, candidate = u + 1/2 where u >= 0 and sigmoid(u) where u < 0;
 element by element S_t = (1 - z) S_(t-1) + z * candidate; output W_o (S_t * silu(W_g h)).  S starts at zero,
