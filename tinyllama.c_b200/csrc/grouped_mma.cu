@@ -3,7 +3,7 @@
 //
 // A block computes a tile of 32 (or, for groups of many rows, 64) rows x 64 columns of ONE group: two warps along the
 // rows, two along the columns.
-// Operand tiles of 32 K-values arrive by cp.async (two stages) in rows padded by 16 bytes, so that ldmatrix reads
+// Operand tiles of 32 K-values arrive by cp.async (three or six stages) in rows padded by 16 bytes, so that ldmatrix reads
 // without bank conflicts; rows past the group's end, columns past N and K-values past K are zero-filled by the copy
 // itself.  Three uses, chosen by MODE:
 //   heads    out[t, h, n] = sum_k a[t, h, k] w[h, n, k]                       (group = head, rows = all T rows)
@@ -43,14 +43,23 @@ struct GmArgs {
 };
 
 // WM: 16-row tiles a warp takes along the rows (1: a block's tile is 32 rows, 2: 64 rows, for groups with many rows).
+// STAGES: operand tiles in flight.  With few rows a group the grid is a few hundred blocks that each stream a slab of
+// weights: six stages keep enough bytes on their way; with many rows three.
+template <int MODE, int WM> struct GmShape {
+  static constexpr int NW = MODE == GM_GATE_UP ? 2 : 1;            // weight tiles per stage (gate and up)
+  static constexpr int TM = GM_TM * WM;
+  static constexpr int STAGES = WM == 1 ? 6 : 3;
+  static constexpr size_t SMEM = (size_t)STAGES * (TM + NW * GM_TN) * GM_LD * sizeof(__nv_bfloat16);
+};
+
 template <int MODE, int WM>
 __global__ void __launch_bounds__(128)
 grouped_mma_kernel(GmArgs p) {
   tlc_pdl(p.a, p.out, p.order, p.offsets, p.tile_off, p.wts);
-  constexpr int NW = MODE == GM_GATE_UP ? 2 : 1;                   // weight tiles per stage (gate and up)
-  constexpr int TM = GM_TM * WM;
-  __shared__ __align__(16) __nv_bfloat16 As[2][TM][GM_LD];
-  __shared__ __align__(16) __nv_bfloat16 Ws[2][NW][GM_TN][GM_LD];
+  constexpr int NW = GmShape<MODE, WM>::NW, TM = GmShape<MODE, WM>::TM, STAGES = GmShape<MODE, WM>::STAGES;
+  extern __shared__ __align__(16) unsigned char gm_smem[];
+  __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(gm_smem);                  // [STAGES][TM][GM_LD]
+  __nv_bfloat16* Ws = As + (size_t)STAGES * TM * GM_LD;                           // [STAGES][NW][GM_TN][GM_LD]
   __shared__ int src_row[TM];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, q4 = lane & 3;
   const int wm = warp & 1, wn = warp >> 1;
@@ -98,7 +107,7 @@ grouped_mma_kernel(GmArgs p) {
 #pragma unroll
     for (int u = 0; u < NW; u++) w_src[u][j] = wg + ((size_t)u * N + n) * K;
   }
-  const uint32_t as_u = (uint32_t)__cvta_generic_to_shared(&As[0][0][0]), ws_u = (uint32_t)__cvta_generic_to_shared(&Ws[0][0][0][0]);
+  const uint32_t as_u = (uint32_t)__cvta_generic_to_shared(As), ws_u = (uint32_t)__cvta_generic_to_shared(Ws);
   auto load = [&](int k0, int buf) {
     const int k = k0 + ac;
     const bool k_ok = k < K;
@@ -123,14 +132,18 @@ grouped_mma_kernel(GmArgs p) {
 #pragma unroll
         for (int e = 0; e < 4; e++) acc[u][i][j][e] = 0.f;
   const int n_k = (K + GM_TK - 1) / GM_TK;
-  load(0, 0);
-  gm_commit();
-  for (int ks = 0; ks < n_k; ks++) {
-    const int buf = ks & 1;
-    if (ks + 1 < n_k) load((ks + 1) * GM_TK, buf ^ 1);
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; st++) {
+    if (st < n_k) load(st * GM_TK, st);
     gm_commit();
-    gm_wait<1>();
-    __syncthreads();
+  }
+  for (int ks = 0; ks < n_k; ks++) {
+    const int buf = ks % STAGES;
+    gm_wait<STAGES - 2>();                     // the tile of this step has landed
+    __syncthreads();                           // ... for every thread, and every warp is done with the step before
+    const int nxt = ks + STAGES - 1;           // its buffer takes the tile STAGES - 1 steps ahead
+    if (nxt < n_k) load(nxt * GM_TK, nxt % STAGES);
+    gm_commit();
 #pragma unroll
     for (int k16 = 0; k16 < GM_TK; k16 += 16) {
       uint32_t af[WM][4];
@@ -151,7 +164,6 @@ grouped_mma_kernel(GmArgs p) {
           }
         }
     }
-    __syncthreads();
   }
   gm_wait<0>();
   // epilogue: this thread holds rows ((wm*WM + i)*16 + g, + 8) and columns wn*32 + 8j + 2q, +1
@@ -186,6 +198,16 @@ grouped_mma_kernel(GmArgs p) {
     }
 }
 
+template <int MODE, int WM>
+static cudaError_t gm_launch(dim3 grid, cudaStream_t stream, const GmArgs& p) {
+  static bool set = false;                     // (more than 48 KB of dynamic shared memory must be asked for once)
+  if (!set) {
+    cudaFuncSetAttribute(grouped_mma_kernel<MODE, WM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GmShape<MODE, WM>::SMEM);
+    set = true;
+  }
+  return tlc_launch(grouped_mma_kernel<MODE, WM>, grid, dim3(128), GmShape<MODE, WM>::SMEM, stream, p);
+}
+
 static inline bool gm_aligned(const void* p, long long ld_elems) { return ((uintptr_t)p % 16) == 0 && ld_elems % 8 == 0; }
 
 // Whether the grouped tensor-core product takes these operands: bfloat16, rows that start on 16-byte boundaries.
@@ -201,9 +223,9 @@ extern "C" int tlc_linear_heads_mma(const void* a, int lda, int a_hs, const void
   p.a = (const __nv_bfloat16*)a; p.w = (const __nv_bfloat16*)w; p.out = out;
   p.lda = lda; p.a_hs = a_hs; p.ldo = ldo; p.o_hs = o_hs; p.T = T; p.N = N; p.K = K; p.out_f32 = out_dtype == TLC_F32;
   if (T >= 512) {                                           // many rows: 64-row tiles
-    tlc_launch(grouped_mma_kernel<GM_HEADS, 2>, dim3((T + 63) / 64, (N + GM_TN - 1) / GM_TN, H), dim3(128), 0, stream, p);
+    gm_launch<GM_HEADS, 2>(dim3((T + 63) / 64, (N + GM_TN - 1) / GM_TN, H), stream, p);
   } else {
-    tlc_launch(grouped_mma_kernel<GM_HEADS, 1>, dim3((T + GM_TM - 1) / GM_TM, (N + GM_TN - 1) / GM_TN, H), dim3(128), 0, stream, p);
+    gm_launch<GM_HEADS, 1>(dim3((T + GM_TM - 1) / GM_TM, (N + GM_TN - 1) / GM_TN, H), stream, p);
   }
   TLC_CHECK_LAUNCH("linear_heads_mma");
   return 0;
@@ -223,12 +245,12 @@ extern "C" int tlc_moe_experts_mma(const void* x, int ldx, const void* wgu, cons
   GmArgs p = {};
   p.order = order; p.offsets = offsets; p.tile_off = tile_off; p.wts = wts; p.E = E; p.top = top; p.T = T;
   p.a = (const __nv_bfloat16*)x; p.lda = ldx; p.w = (const __nv_bfloat16*)wgu; p.out = act; p.N = F; p.K = D;
-  if (tile_rows == 64) tlc_launch(grouped_mma_kernel<GM_GATE_UP, 2>, dim3(tiles, (F + GM_TN - 1) / GM_TN), dim3(128), 0, stream, p);
-  else tlc_launch(grouped_mma_kernel<GM_GATE_UP, 1>, dim3(tiles, (F + GM_TN - 1) / GM_TN), dim3(128), 0, stream, p);
+  if (tile_rows == 64) gm_launch<GM_GATE_UP, 2>(dim3(tiles, (F + GM_TN - 1) / GM_TN), stream, p);
+  else gm_launch<GM_GATE_UP, 1>(dim3(tiles, (F + GM_TN - 1) / GM_TN), stream, p);
   TLC_CHECK_LAUNCH("moe_gate_up_mma");
   p.a = (const __nv_bfloat16*)act; p.lda = F; p.w = (const __nv_bfloat16*)wd; p.out = y; p.N = D; p.K = F;
-  if (tile_rows == 64) tlc_launch(grouped_mma_kernel<GM_DOWN, 2>, dim3(tiles, (D + GM_TN - 1) / GM_TN), dim3(128), 0, stream, p);
-  else tlc_launch(grouped_mma_kernel<GM_DOWN, 1>, dim3(tiles, (D + GM_TN - 1) / GM_TN), dim3(128), 0, stream, p);
+  if (tile_rows == 64) gm_launch<GM_DOWN, 2>(dim3(tiles, (D + GM_TN - 1) / GM_TN), stream, p);
+  else gm_launch<GM_DOWN, 1>(dim3(tiles, (D + GM_TN - 1) / GM_TN), stream, p);
   TLC_CHECK_LAUNCH("moe_down_mma");
   return 0;
 }
