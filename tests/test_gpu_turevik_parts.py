@@ -121,6 +121,26 @@ def test_gated_activation(act):
     assert np.abs(out.cpu().numpy() - want).max() <= 2e-6 * np.abs(want).max()
 
 
+@pytest.mark.parametrize("act", ["silu", "gelu_tanh"])
+@pytest.mark.parametrize("dtype,D,F", [("bfloat16", 256, 2048), ("bfloat16", 64, 40), ("bfloat16", 44, 28), ("float32", 64, 40)])
+def test_gated_feed_forward_with_either_activation(act, dtype, D, F):
+    """The dense feed-forward part with its activation in the product's epilogue (bfloat16, widths that are multiples
+    of 8: the kernels for 1..32, 17..128 and more rows) or as a kernel of its own."""
+    g = np.random.default_rng(12)
+    W = {"f.gate": draw(g, (F, D), 0.1, dtype), "f.up": draw(g, (F, D), 0.1, dtype), "f.down": draw(g, (D, F), 0.1, dtype)}
+    part = PartSpec("feed_forward", "swiglu", dict(hidden=D, intermediate=F, prefix="f.", act=act,
+                                                   names=dict(gate="gate", up="up", down="down"))).build()
+    part.bind({k: torch.tensor(v, dtype=DT[dtype]) for k, v in W.items()}, DT[dtype], "cuda")
+    f = plain.gelu_tanh if act == "gelu_tanh" else plain.silu
+    for T in (1, 20, 40, 100, 300):
+        x = draw(g, (T, D), 2.0, dtype)
+        out = torch.zeros((T, D), dtype=torch.float32, device="cuda")
+        part.forward(dev(x, DT[dtype]), out, accumulate=False)
+        want = plain.gated_ff(x, W, "f.", f, rnd_of(dtype))
+        err = np.abs(out.cpu().numpy() - want).max()
+        assert err <= (3e-5 if dtype == "float32" else 2e-2) * np.abs(want).max(), f"{act} {T} rows: error {err:.3e}"
+
+
 @pytest.mark.parametrize("dtype,T,K,pad,N", [("float32", 45, 20, 5, 37), ("bfloat16", 45, 20, 5, 37), ("bfloat16", 1, 24, 8, 37),
                                              ("bfloat16", 100, 72, 8, 70), ("bfloat16", 33, 16, 0, 64)])
 def test_product_per_head(dtype, T, K, pad, N):

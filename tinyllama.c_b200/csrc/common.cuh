@@ -131,6 +131,19 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x));
 // full-precision division costs several times as much.
 __device__ __forceinline__ float silu_quick(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 template <bool QUICK> __device__ __forceinline__ float silu_of(float x) { return QUICK ? silu_quick(x) : silu_f(x); }
+// GELU in its tanh form, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); the quick one takes tanh(y) = 1 - 2 / (1 + e^(2y))
+// from the special-function unit.
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float gelu_tanh_quick(float z) {
+  const float y = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+  return z - __fdividef(z, 1.0f + __expf(2.0f * y));          // 0.5 z (1 + tanh y) = z (1 - 1 / (1 + e^(2y)))
+}
+// The activation of a gated product's fused epilogue by its code (TLC_ACT_SILU, TLC_ACT_GELU_TANH).
+template <bool QUICK> __device__ __forceinline__ float glu_act_of(int act, float z) {
+  return act == 1 ? (QUICK ? gelu_tanh_quick(z) : gelu_tanh_f(z)) : silu_of<QUICK>(z);
+}
 // softplus with the reference's cut-over (cpu_op.c:354-356)
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 

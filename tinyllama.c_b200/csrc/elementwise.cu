@@ -315,9 +315,6 @@ extern "C" int tlc_gated_rmsnorm(const float* y, const float* y2, const void* z,
 // ---- gated product: out = act(gate) * up, gate|up side by side in one row -----------------
 // interleave: gate and up come in groups of 16 columns (8 gates, then their 8 ups) instead of as two halves.
 // ACT 0: SiLU; 1: the tanh form of GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
-__device__ __forceinline__ float gelu_tanh_f(float z) {
-  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-}
 template <int ACT> __device__ __forceinline__ float glu_act(float z) { return ACT == 1 ? gelu_tanh_f(z) : silu_f(z); }
 
 template <typename TI, typename T, int ACT>

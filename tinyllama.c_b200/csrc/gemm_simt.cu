@@ -298,7 +298,7 @@ gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_
         if (nu < N && m < M) {
           if (colscale) { vg *= colscale[ng]; vu *= colscale[nu]; }
           if (colbias) { vg += colbias[ng]; vu += colbias[nu]; }
-          out[(size_t)m * ldo + (n0 >> 1) + (ln >> 2)] = from_f32<TO>(silu_f(vg) * vu);
+          out[(size_t)m * ldo + (n0 >> 1) + (ln >> 2)] = from_f32<TO>(glu_act_of<false>(accumulate, vg) * vu);   // (the activation's code)
         }
       }
       continue;
@@ -414,11 +414,11 @@ extern "C" int tlc_linear_skinny(const void* a, int lda, const void* w, int ldw,
 extern "C" void tlc_linear_skinny_pairs(int on) { g_skinny_pairs = on; }
 
 extern "C" int tlc_linear_skinny_swiglu(const void* a, int lda, const void* w, int ldw, void* out, int out_dtype, int ldo,
-                                        const float* colscale, const float* colbias, int M, int N, int K,
+                                        const float* colscale, const float* colbias, int M, int N, int K, int act,
                                         cudaStream_t stream) {
   if (out_dtype == TLC_F32)
-    return launch_skinny_mma<float, true>(a, lda, w, ldw, out, ldo, colscale, colbias, 0, M, N, K, stream);
+    return launch_skinny_mma<float, true>(a, lda, w, ldw, out, ldo, colscale, colbias, act, M, N, K, stream);
   if (out_dtype == TLC_BF16)
-    return launch_skinny_mma<__nv_bfloat16, true>(a, lda, w, ldw, out, ldo, colscale, colbias, 0, M, N, K, stream);
+    return launch_skinny_mma<__nv_bfloat16, true>(a, lda, w, ldw, out, ldo, colscale, colbias, act, M, N, K, stream);
   return tlc_fail(-1, "linear: unknown output dtype %d", out_dtype);
 }

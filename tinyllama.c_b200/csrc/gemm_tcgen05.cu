@@ -31,7 +31,7 @@ int tlc_linear_few_rows_run(const void* a, int lda, const void* w, int ldw, void
                             const float* colscale, const float* colbias, int accumulate, int M, int N, int K,
                             cudaStream_t stream);
 int tlc_linear_few_rows_swiglu(const void* a, int lda, const void* w, int ldw, void* out, int out_dtype, int ldo,
-                               const float* colscale, const float* colbias, int M, int N, int K, cudaStream_t stream);
+                               const float* colscale, const float* colbias, int M, int N, int K, int act, cudaStream_t stream);
 
 namespace {
 
@@ -317,7 +317,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               vg = vg * sc[jg] + sc[BN + jg];
               vu = vu * sc[jg + 8] + sc[BN + jg + 8];
             }
-            o16[f] = silu_quick(vg) * vu;
+            o16[f] = glu_act_of<true>(accumulate, vg) * vu;       // (with SWIGLU the argument carries the activation's code)
           }
           if (m < M) {
             TO* dst = out + (size_t)m * ldo + oc0;
@@ -795,46 +795,48 @@ extern "C" int tlc_linear_tcgen05_ok(int a_dtype, int lda, const void* a, int w_
          ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0);
 }
 
-// The fused feed-forward front: out[M, N/2] = silu(gate) * up, where the rows of w come in groups of
+// The fused feed-forward front: out[M, N/2] = act(gate) * up (act: SiLU or the tanh form of GELU; the kernels' SWIGLU
+// instantiations take its code in the argument that is `accumulate` elsewhere), where the rows of w come in groups of
 // 16 (8 gate rows, then their 8 up rows) and gate/up = (a w^T) * colscale + colbias.  Returns 1 if no
 // kernel takes these operands (the caller then runs the product and the activation separately).
 extern "C" int tlc_linear_swiglu(const void* a, int a_dtype, int lda, const void* w, int w_dtype, int ldw, void* out,
                                  int out_dtype, int ldo, const float* colscale, const float* colbias, int M, int N, int K,
-                                 int min_rows_for_tensor_cores, cudaStream_t stream) {
+                                 int min_rows_for_tensor_cores, int act, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
+  TLC_REQUIRE(act == TLC_ACT_SILU || act == TLC_ACT_GELU_TANH, "linear_swiglu: unknown activation %d", act);
   if (N % 16 != 0 || !tlc_linear_tcgen05_ok(a_dtype, lda, a, w_dtype, ldw, w, K)) return 1;
   TLC_REQUIRE(K > 0 && lda >= K && ldw >= K && ldo >= N / 2, "linear: bad sizes M=%d N=%d K=%d lda=%d ldw=%d ldo=%d", M, N, K,
               lda, ldw, ldo);
   if (out_dtype != TLC_F32 && out_dtype != TLC_BF16) return tlc_fail(-1, "linear: unknown output dtype %d", out_dtype);
   if (min_rows_for_tensor_cores <= 128 && tlc_linear_few_rows_ok(a_dtype, lda, a, w_dtype, ldw, w, M, N, K)) {
     if (int rc = init_once()) return rc;
-    return tlc_linear_few_rows_swiglu(a, lda, w, ldw, out, out_dtype, ldo, colscale, colbias, M, N, K, stream);
+    return tlc_linear_few_rows_swiglu(a, lda, w, ldw, out, out_dtype, ldo, colscale, colbias, M, N, K, act, stream);
   }
   if (M <= 32 && tlc_linear_skinny_ok(a_dtype, lda, a, w_dtype, ldw, w, M, K))
-    return tlc_linear_skinny_swiglu(a, lda, w, ldw, out, out_dtype, ldo, colscale, colbias, M, N, K, stream);
+    return tlc_linear_skinny_swiglu(a, lda, w, ldw, out, out_dtype, ldo, colscale, colbias, M, N, K, act, stream);
   if (M < min_rows_for_tensor_cores) return 1;
   if (int rc = init_once()) return rc;
   CUtensorMap ma, mb;
   if (int rc = get_map(a, M, K, lda, BM, &ma)) return rc;
   if (pick_pairs(M, N)) {
     if (int rc = get_map(w, N, K, ldw, PAIR_BN / 2, &mb)) return rc;
-    return out_dtype == TLC_F32 ? launch_pairs<float, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream)
-                                : launch_pairs<__nv_bfloat16, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream);
+    return out_dtype == TLC_F32 ? launch_pairs<float, true>(ma, mb, out, ldo, colscale, colbias, act, M, N, K, stream)
+                                : launch_pairs<__nv_bfloat16, true>(ma, mb, out, ldo, colscale, colbias, act, M, N, K, stream);
   }
   const int bn = pick_tile(M, N);
   if (bn == 256) {
     if (int rc = get_map(w, N, K, ldw, 256, &mb)) return rc;
-    return out_dtype == TLC_F32 ? launch<float, 256, 4, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream)
-                                : launch<__nv_bfloat16, 256, 4, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream);
+    return out_dtype == TLC_F32 ? launch<float, 256, 4, true>(ma, mb, out, ldo, colscale, colbias, act, M, N, K, stream)
+                                : launch<__nv_bfloat16, 256, 4, true>(ma, mb, out, ldo, colscale, colbias, act, M, N, K, stream);
   }
   if (bn == 64) {
     if (int rc = get_map(w, N, K, ldw, 64, &mb)) return rc;
-    return out_dtype == TLC_F32 ? launch<float, 64, 8, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream)
-                                : launch<__nv_bfloat16, 64, 8, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream);
+    return out_dtype == TLC_F32 ? launch<float, 64, 8, true>(ma, mb, out, ldo, colscale, colbias, act, M, N, K, stream)
+                                : launch<__nv_bfloat16, 64, 8, true>(ma, mb, out, ldo, colscale, colbias, act, M, N, K, stream);
   }
   if (int rc = get_map(w, N, K, ldw, 128, &mb)) return rc;
-  return out_dtype == TLC_F32 ? launch<float, 128, 6, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream)
-                              : launch<__nv_bfloat16, 128, 6, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream);
+  return out_dtype == TLC_F32 ? launch<float, 128, 6, true>(ma, mb, out, ldo, colscale, colbias, act, M, N, K, stream)
+                              : launch<__nv_bfloat16, 128, 6, true>(ma, mb, out, ldo, colscale, colbias, act, M, N, K, stream);
 }
 
 extern "C" int tlc_linear(const void* a, int a_dtype, int lda, const void* w, int w_dtype, int ldw, void* out,

@@ -196,7 +196,7 @@ gemm_few_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         v = v * cs + cb;
         if (SWIGLU) {
           v2 = v2 * cs2 + cb2;
-          out[(size_t)m * ldo + (n0 >> 1) + ((row >> 4) << 3) + (row & 7)] = from_f32<TO>(silu_f(v) * v2);
+          out[(size_t)m * ldo + (n0 >> 1) + ((row >> 4) << 3) + (row & 7)] = from_f32<TO>(glu_act_of<false>(accumulate, v) * v2);      // (with SWIGLU the argument carries the activation's code)
         } else {
           TO* o = out + (size_t)m * ldo + n;
           if (accumulate) v += to_f32(*o);
@@ -323,6 +323,6 @@ int tlc_linear_few_rows_run(const void* a, int lda, const void* w, int ldw, void
 }
 
 int tlc_linear_few_rows_swiglu(const void* a, int lda, const void* w, int ldw, void* out, int out_dtype, int ldo,
-                               const float* colscale, const float* colbias, int M, int N, int K, cudaStream_t stream) {
-  return run_few<true>(a, lda, w, ldw, out, out_dtype, ldo, colscale, colbias, 0, M, N, K, g_force_split, stream);
+                               const float* colscale, const float* colbias, int M, int N, int K, int act, cudaStream_t stream) {
+  return run_few<true>(a, lda, w, ldw, out, out_dtype, ldo, colscale, colbias, act, M, N, K, g_force_split, stream);
 }

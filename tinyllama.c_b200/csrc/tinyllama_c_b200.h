@@ -28,6 +28,8 @@
 #define TLC_F32 0
 #define TLC_BF16 1
 #define TLC_PAGE 64
+#define TLC_ACT_SILU 0       /* activations of gated products: z * sigmoid(z) */
+#define TLC_ACT_GELU_TANH 1  /* 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) */
 
 #ifdef __cplusplus
 extern "C" {
@@ -100,11 +102,12 @@ int tlc_rmsnorm_add(const float* parts, int n_parts, const float* extra, const f
 int tlc_linear(const void* a, int a_dtype, int lda, const void* w, int w_dtype, int ldw, void* out,
                int out_dtype, int ldo, const float* colscale, const float* colbias, int accumulate, int M,
                int N, int K, int min_rows_for_tensor_cores, cudaStream_t stream);
-/* out[M, N/2] = silu(gate) * up where the rows of w come in groups of 16 (8 gate rows, their 8 up rows).
- * Returns 1 when no fused kernel takes the operands (run tlc_linear and tlc_swiglu instead). */
+/* out[M, N/2] = act(gate) * up where the rows of w come in groups of 16 (8 gate rows, their 8 up rows); act is
+ * TLC_ACT_SILU or TLC_ACT_GELU_TANH.  Returns 1 when no fused kernel takes the operands (run tlc_linear and tlc_glu
+ * instead). */
 int tlc_linear_swiglu(const void* a, int a_dtype, int lda, const void* w, int w_dtype, int ldw, void* out,
                       int out_dtype, int ldo, const float* colscale, const float* colbias, int M, int N, int K,
-                      int min_rows_for_tensor_cores, cudaStream_t stream);
+                      int min_rows_for_tensor_cores, int act, cudaStream_t stream);
 int tlc_linear_simt(const void* a, int a_dtype, int lda, const void* w, int w_dtype, int ldw, void* out,
                     int out_dtype, int ldo, const float* colscale, const float* colbias, int accumulate,
                     int M, int N, int K, cudaStream_t stream);
@@ -121,7 +124,7 @@ int tlc_linear_skinny(const void* a, int lda, const void* w, int ldw, void* out,
                       const float* colscale, const float* colbias, int accumulate, int M, int N, int K,
                       cudaStream_t stream);
 int tlc_linear_skinny_swiglu(const void* a, int lda, const void* w, int ldw, void* out, int out_dtype, int ldo,
-                             const float* colscale, const float* colbias, int M, int N, int K,
+                             const float* colscale, const float* colbias, int M, int N, int K, int act,
                              cudaStream_t stream);
 int tlc_linear_tcgen05_ok(int a_dtype, int lda, const void* a, int w_dtype, int ldw, const void* w, int K);
 /* Test hooks: force the tile width (0, 64, 128, 256) / how many blocks share a tile's K-steps (0 = choose). */

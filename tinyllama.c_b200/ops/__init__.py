@@ -46,11 +46,11 @@ _SIGNATURES = {
     "tlc_swiglu": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _i, _vp]),
     "tlc_gather_rows": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
     "tlc_linear": (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
-    "tlc_linear_swiglu": (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "tlc_linear_swiglu": (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "tlc_linear_simt": (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
     "tlc_linear_skinny_ok": (_i, [_i, _i, _vp, _i, _i, _vp, _i, _i]),
     "tlc_linear_skinny": (_i, [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
-    "tlc_linear_skinny_swiglu": (_i, [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _vp]),
+    "tlc_linear_skinny_swiglu": (_i, [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
     "tlc_linear_tcgen05_ok": (_i, [_i, _i, _vp, _i, _i, _vp, _i]),
     "tlc_linear_tile_override": (None, [_i]),
     "tlc_linear_split_override": (None, [_i]),
@@ -412,10 +412,12 @@ def linear_pairs() -> int:
 
 
 def linear_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, colscale: Optional[torch.Tensor] = None,
-                  colbias: Optional[torch.Tensor] = None) -> None:
-    """out[M, F] = silu(gate) * up with gate | up = (a w^T) * colscale + colbias, the 2F rows of w in
-    groups of 16 (8 gate rows followed by their 8 up rows).  One kernel where the operands allow it
-    (bfloat16, 16-byte aligned rows), else the product and the activation one after the other."""
+                  colbias: Optional[torch.Tensor] = None, act: str = "silu") -> None:
+    """out[M, F] = act(gate) * up with gate | up = (a w^T) * colscale + colbias, the 2F rows of w in
+    groups of 16 (8 gate rows followed by their 8 up rows); act: "silu" or "gelu_tanh".  One kernel where the
+    operands allow it (bfloat16, 16-byte aligned rows), else the product and the activation one after the other."""
+    if act not in GLU_ACTS:
+        raise KernelError(f"linear_swiglu: unknown activation '{act}'; known: {sorted(GLU_ACTS)}")
     _gpu(a, w, out, colscale, colbias)
     M, K = a.shape
     N = w.shape[0]
@@ -428,12 +430,12 @@ def linear_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, colscale:
     _launches += 1
     rc = lib.tlc_linear_swiglu(a.data_ptr(), dtype_code(a.dtype), _rows(a, "linear input"), w.data_ptr(), dtype_code(w.dtype),
                                _rows(w, "linear weight"), out.data_ptr(), dtype_code(out.dtype), N // 2, _p(colscale),
-                               _p(colbias), M, N, K, TENSOR_CORE_MIN_ROWS, _stream())
+                               _p(colbias), M, N, K, TENSOR_CORE_MIN_ROWS, GLU_ACTS[act], _stream())
     if rc == 1:                                   # no fused kernel for these operands
         _launches -= 1
         gu = torch.empty((M, N), dtype=torch.float32, device=a.device)
         linear(a, w, gu, colscale, colbias)
-        swiglu(gu, out, interleaved=True)
+        glu(gu, out, act, interleaved=True)
     elif rc != 0:
         raise KernelError(f"tlc_linear_swiglu: {lib.tlc_last_error().decode()}")
 

@@ -61,8 +61,8 @@ class SwiGLU(Part):
         """Adds the result into `residual` (float32 [T, D]), or overwrites it with accumulate False."""
         T = normed.shape[0]
         act = scratch_buf("swiglu.act", (T, self.F), normed.dtype, normed.device)
-        if self.interleaved and self.act == "silu":
-            ops.linear_swiglu(normed, self.gate_up.weight, act, self.gate_up.colscale, self.gate_up.colbias)
+        if self.interleaved:
+            ops.linear_swiglu(normed, self.gate_up.weight, act, self.gate_up.colscale, self.gate_up.colbias, self.act)
         else:
             gu = scratch_buf("swiglu.gate_up", (T, 2 * self.F), torch.float32, normed.device)
             self.gate_up.forward(normed, gu)
