@@ -58,15 +58,23 @@ def _gate_up(gate_up, interleaved):
     return r[:, :, 0, :].reshape(-1, F), r[:, :, 1, :].reshape(-1, F)
 
 
-def linear_swiglu(a, w, out, colscale=None, colbias=None):
+def linear_swiglu(a, w, out, colscale=None, colbias=None, act="silu"):
     gu = torch.empty((a.shape[0], w.shape[0]), dtype=torch.float64)
     linear(a, w, gu, colscale, colbias)
-    swiglu(gu, out, interleaved=True)
+    glu(gu, out, act, interleaved=True)
+
+
+def glu(gate_up, out, act="silu", interleaved=False):
+    g, u = _gate_up(gate_up, interleaved)
+    if act == "gelu_tanh":
+        a = 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
+    else:
+        a = g / (1.0 + torch.exp(-g))
+    out.copy_((a * u).to(out.dtype))
 
 
 def swiglu(gate_up, out, interleaved=False):
-    g, u = _gate_up(gate_up, interleaved)
-    out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
+    glu(gate_up, out, "silu", interleaved)
 
 
 def gather_rows(x, rows, out):
@@ -235,7 +243,7 @@ def sample(logits, work, history, uniforms, temperature, top_k, top_p, min_p, re
                             temperature, top_k, top_p, min_p, repeat_penalty, frequency_penalty, presence_penalty)
 
 
-ALL = ["embed", "rmsnorm", "gated_rmsnorm", "swiglu", "gather_rows", "linear", "linear_swiglu", "rope_kv_store", "attention",
+ALL = ["embed", "rmsnorm", "gated_rmsnorm", "swiglu", "glu", "gather_rows", "linear", "linear_swiglu", "rope_kv_store", "attention",
        "mamba_conv", "ssm_scan", "argmax", "sample"]
 
 
