@@ -144,6 +144,25 @@ __device__ __forceinline__ float gelu_tanh_quick(float z) {
 template <bool QUICK> __device__ __forceinline__ float glu_act_of(int act, float z) {
   return act == 1 ? (QUICK ? gelu_tanh_quick(z) : gelu_tanh_f(z)) : silu_of<QUICK>(z);
 }
+// One (token, expert) pair's activation in an expert's gated feed-forward, from the 32-bit results g and u of the gate
+// and up products and the pair's routing weight w.  w_out 0: the expert is fed the token scaled by w (gate and up are
+// linear, so w multiplies their results); 1: w multiplies what the expert returns (the down product is linear, so it
+// multiplies the activation).  act TLC_ACT_SILU / TLC_ACT_GELU_TANH: act(g) * u; TLC_ACT_SWISH_CLAMPED: with g cut off
+// above `limit` and u held within +-limit, g * sigmoid(alpha g) * (u + 1).
+template <bool QUICK> __device__ __forceinline__ float moe_pair_act(int act, int w_out, float limit, float alpha, float w, float g,
+                                                                  float u) {
+  if (!w_out) { g *= w; u *= w; }
+  float y;
+  if (act == TLC_ACT_SWISH_CLAMPED) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    const float sg = QUICK ? __fdividef(1.0f, 1.0f + __expf(-alpha * g)) : 1.0f / (1.0f + expf(-alpha * g));
+    y = g * sg * (u + 1.0f);
+  } else {
+    y = glu_act_of<QUICK>(act, g) * u;
+  }
+  return w_out ? y * w : y;
+}
 // softplus with the reference's cut-over (cpu_op.c:354-356)
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 

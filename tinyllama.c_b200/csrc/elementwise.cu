@@ -48,12 +48,12 @@ extern "C" int tlc_embed(const int* tokens, const void* table, int table_dtype, 
 #define RMS_MAX_PER_THREAD 16
 template <typename TO>
 __global__ void __launch_bounds__(256)
-rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+rmsnorm_kernel(const float* __restrict__ x, int x_ld, const int* __restrict__ rows, const float* __restrict__ w,
                float eps, int D, TO* __restrict__ out) {
   tlc_pdl(x, rows, out);
   __shared__ float red[33];
   const int r = blockIdx.x;
-  const float* xr = x + (size_t)(rows ? rows[r] : r) * D;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * x_ld;
   float ss = 0.f;
   if (D <= 256 * RMS_MAX_PER_THREAD) {
     float v[RMS_MAX_PER_THREAD];
@@ -99,7 +99,7 @@ template <> struct Out4<__nv_bfloat16> {
 
 template <typename TO, int NT, int PT>
 __global__ void __launch_bounds__(NT)
-rmsnorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+rmsnorm_vec_kernel(const float* __restrict__ x, int x_ld, const int* __restrict__ rows, const float* __restrict__ w,
                    float eps, int D, TO* __restrict__ out) {
   asm volatile("griddepcontrol.launch_dependents;");
   __shared__ float red[33];
@@ -112,7 +112,7 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows, co
   }
   tlc_wait(x, rows, out);
   const int r = blockIdx.x;
-  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * D);
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * x_ld);
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < PT; i++) {
@@ -153,20 +153,21 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows, co
   else { LAUNCH(1024, 4); }
 constexpr int VEC_MANY_ROWS = 512;            // from this many rows on
 
-extern "C" int tlc_rmsnorm(const float* x, const int* rows, const float* w, float eps, int R, int D, void* out,
+extern "C" int tlc_rmsnorm(const float* x, int x_ld, const int* rows, const float* w, float eps, int R, int D, void* out,
                            int out_dtype, cudaStream_t stream) {
   if (R == 0) return 0;
-  if (D % 4 == 0 && D <= 16384 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+  TLC_REQUIRE(x_ld >= D, "rmsnorm: rows of %d values with a stride of %d", D, x_ld);
+  if (D % 4 == 0 && x_ld % 4 == 0 && D <= 16384 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)out % 16) == 0) {
     const int n4 = D / 4;
 #define TLC_RMS_LAUNCH(NT, PT)                                                                                        \
-  TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(rmsnorm_vec_kernel<TO, NT, PT>, dim3(R), dim3(NT), 0, stream, x, rows, w, \
+  TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(rmsnorm_vec_kernel<TO, NT, PT>, dim3(R), dim3(NT), 0, stream, x, x_ld, rows, w, \
                                                eps, D, (TO*)out))
     if (R >= VEC_MANY_ROWS) { TLC_VEC_SHAPES_MANY(n4, TLC_RMS_LAUNCH) } else { TLC_VEC_SHAPES(n4, TLC_RMS_LAUNCH) }
 #undef TLC_RMS_LAUNCH
     TLC_CHECK_LAUNCH("rmsnorm");
     return 0;
   }
-  TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(rmsnorm_kernel<TO>, dim3(R), dim3(256), 0, stream, x, rows, w, eps, D, (TO*)out));
+  TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(rmsnorm_kernel<TO>, dim3(R), dim3(256), 0, stream, x, x_ld, rows, w, eps, D, (TO*)out));
   TLC_CHECK_LAUNCH("rmsnorm");
   return 0;
 }

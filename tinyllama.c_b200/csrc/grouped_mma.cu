@@ -40,6 +40,8 @@ struct GmArgs {
                                // bfloat16; down: y [pairs, N] float
   const int* order; const int* offsets; const int* tile_off; const float* wts;
   int lda, a_hs, ldo, o_hs, T, N, K, E, top, out_f32;
+  int act, w_out;              // gate_up: the activation's code and where the pair's weight goes (moe_pair_act)
+  float limit, alpha;
 };
 
 // WM: 16-row tiles a warp takes along the rows (1: a block's tile is 32 rows, 2: 64 rows, for groups with many rows).
@@ -187,7 +189,8 @@ grouped_mma_kernel(GmArgs p) {
           const float v = acc[0][i][j][2 * e + c];
           if (MODE == GM_GATE_UP) {
             const float u = acc[NW - 1][i][j][2 * e + c];
-            reinterpret_cast<__nv_bfloat16*>(p.out)[orow + n] = __float2bfloat16_rn(silu_quick(wgt * v) * (wgt * u));
+            reinterpret_cast<__nv_bfloat16*>(p.out)[orow + n] =
+                __float2bfloat16_rn(moe_pair_act<true>(p.act, p.w_out, p.limit, p.alpha, wgt, v, u));
           } else if (MODE == GM_DOWN || p.out_f32) {
             reinterpret_cast<float*>(p.out)[orow + n] = v;
           } else {
@@ -235,8 +238,9 @@ extern "C" int tlc_linear_heads_mma(const void* a, int lda, int a_hs, const void
 // [T*top, F] bfloat16 scratch, y [T*top, D] float.
 extern "C" int tlc_moe_experts_mma(const void* x, int ldx, const void* wgu, const void* wd, const int* order, const int* offsets,
                                    const int* tile_off, const float* wts, int T, int E, int top, int F, int D, void* act, float* y,
-                                   int tile_rows, cudaStream_t stream) {
+                                   int tile_rows, int act_code, int w_out, float limit, float alpha, cudaStream_t stream) {
   if (T == 0) return 0;
+  TLC_REQUIRE(act_code >= TLC_ACT_SILU && act_code <= TLC_ACT_SWISH_CLAMPED, "moe_experts_mma: unknown activation %d", act_code);
   TLC_REQUIRE(tile_rows == 32 || tile_rows == 64, "moe_experts_mma: tiles of %d rows are not built (32 or 64, as the routing was made)", tile_rows);
   TLC_REQUIRE(D % 8 == 0 && F % 8 == 0 && gm_aligned(x, ldx) && gm_aligned(wgu, D) && gm_aligned(wd, F) && gm_aligned(act, F),
               "moe_experts_mma: operands are not aligned for 16-byte copies");
@@ -244,6 +248,7 @@ extern "C" int tlc_moe_experts_mma(const void* x, int ldx, const void* wgu, cons
   const int tiles = (int)(pairs / tile_rows + (pairs < E ? pairs : E));
   GmArgs p = {};
   p.order = order; p.offsets = offsets; p.tile_off = tile_off; p.wts = wts; p.E = E; p.top = top; p.T = T;
+  p.act = act_code; p.w_out = w_out; p.limit = limit; p.alpha = alpha;
   p.a = (const __nv_bfloat16*)x; p.lda = ldx; p.w = (const __nv_bfloat16*)wgu; p.out = act; p.N = F; p.K = D;
   if (tile_rows == 64) gm_launch<GM_GATE_UP, 2>(dim3(tiles, (F + GM_TN - 1) / GM_TN), stream, p);
   else gm_launch<GM_GATE_UP, 1>(dim3(tiles, (F + GM_TN - 1) / GM_TN), stream, p);

@@ -16,20 +16,21 @@
 #include "common.cuh"
 
 // ---- per row: rotate, norm, store ---------------------------------------------------------------------
-// proj [T, ld] float: the row's queries at q_off, H heads of (dn | r); its down-projection (R | r) at dkv_off, or
-// dkv_off < 0 for a layer that reads another layer's rows.  Writes qn [T, H*dn] (the unrotated query parts), the
+// qproj [T, ldq] float: the row's queries at q_off, H heads of (dn | r); proj [T, ld] float: its down-projection (R | r)
+// at dkv_off, or dkv_off < 0 for a layer that reads another layer's rows (the two may be one buffer).  Writes qn [T, H*dn] (the unrotated query parts), the
 // rotated parts into the last r columns of every head of qa [T, H*(R+r)], and, with a down-projection, the cache row.
 template <typename TC>
 __global__ void __launch_bounds__(512)
-latent_prepare_kernel(const float* __restrict__ proj, int ld, int q_off, int dkv_off, const float* __restrict__ cw, float eps,
+latent_prepare_kernel(const float* __restrict__ qproj, int ldq, int q_off, const float* __restrict__ proj, int ld, int dkv_off,
+                      const float* __restrict__ cw, float eps,
                       const float* __restrict__ inv_freq, int rot, const int* __restrict__ positions,
                       const int* __restrict__ row_seq, const int* __restrict__ slots, const int* __restrict__ block_table,
                       int max_pages, TC* __restrict__ pages, TC* __restrict__ qn, TC* __restrict__ qa, int H, int dn, int r,
                       int R) {
-  tlc_pdl(proj, pages, qn, qa);
+  tlc_pdl(qproj, proj, pages, qn, qa);
   __shared__ float red[33];
   const int t = blockIdx.x;
-  const float* pr = proj + (size_t)t * ld;
+  const float* pr = qproj + (size_t)t * ldq;
   const int pos = positions[t];
   const float fpos = (float)pos;
   const int hw = dn + r, aw = R + r;
@@ -55,7 +56,7 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, int q_off, int dkv
     }
   }
   if (dkv_off < 0) return;
-  const float* cr = pr + dkv_off;
+  const float* cr = proj + (size_t)t * ld + dkv_off;
   float ss = 0.f;
   for (int d = threadIdx.x; d < R; d += blockDim.x) { const float v = cr[d]; ss += v * v; }
   ss = block_sum(ss, red);
@@ -78,14 +79,15 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, int q_off, int dkv
   }
 }
 
-extern "C" int tlc_latent_prepare(const float* proj, int ld, int q_off, int dkv_off, const float* cw, float eps,
+extern "C" int tlc_latent_prepare(const float* qproj, int ldq, int q_off, const float* proj, int ld, int dkv_off, const float* cw,
+                                  float eps,
                                   const float* inv_freq, int rot, const int* positions, const int* row_seq, const int* slots,
                                   const int* block_table, int max_pages, void* pages, void* qn, void* qa, int dtype, int T, int H,
                                   int dn, int r, int R, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= r, "latent_prepare: %d rotated dimensions of %d", rot, r);
   const int nt = T < 256 ? 512 : 128;                       // few rows: more threads a row
-  TLC_DISPATCH_DTYPE(dtype, TC, tlc_launch(latent_prepare_kernel<TC>, dim3(T), dim3(nt), 0, stream, proj, ld, q_off, dkv_off, cw, eps,
+  TLC_DISPATCH_DTYPE(dtype, TC, tlc_launch(latent_prepare_kernel<TC>, dim3(T), dim3(nt), 0, stream, qproj, ldq, q_off, proj, ld, dkv_off, cw, eps,
                                            inv_freq, rot, positions, row_seq, slots, block_table, max_pages, (TC*)pages, (TC*)qn,
                                            (TC*)qa, H, dn, r, R));
   TLC_CHECK_LAUNCH("latent_prepare");
@@ -101,7 +103,7 @@ __global__ void __launch_bounds__(128)
 latent_attention_warp_kernel(const TC* __restrict__ qa, const TC* __restrict__ pages, const float* __restrict__ sink,
                              const int* __restrict__ block_table, int max_pages, const int* __restrict__ positions,
                              const int* __restrict__ row_seq, const int* __restrict__ slots, TC* __restrict__ out, int H, int R,
-                             int r, float scale) {
+                             int r, float scale, int window) {
   tlc_pdl(qa, pages, out);
   extern __shared__ float sh[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -114,11 +116,13 @@ latent_attention_warp_kernel(const TC* __restrict__ qa, const TC* __restrict__ p
   __syncwarp();
   const int n_keys = positions[t] + 1;
   const int* table = block_table + (size_t)slots[row_seq[t]] * max_pages;
-  float m = sink[h], l = 1.0f;             // the sink: exp(sink - m) with m = sink
+  float m = -INFINITY, l = 0.f;
+  if (sink) { m = sink[h]; l = 1.0f; }     // the sink: exp(sink - m) with m = sink
+  const int k_first = window > 0 ? max(0, n_keys - window) : 0;     // a window: the last `window` keys
   float acc[LAT_MAXV];
 #pragma unroll
   for (int i = 0; i < LAT_MAXV; i++) acc[i] = 0.f;
-  for (int k0 = 0; k0 < n_keys; k0 += 32) {
+  for (int k0 = k_first; k0 < n_keys; k0 += 32) {
     const int kp = k0 + lane;
     float s = -INFINITY;
     if (kp < n_keys) {
@@ -157,7 +161,7 @@ latent_attention_warp_kernel(const TC* __restrict__ qa, const TC* __restrict__ p
 
 extern "C" int tlc_latent_attention(const void* qa, const void* pages, int dtype, const float* sink, const int* block_table,
                                     int max_pages, const int* positions, const int* row_seq, const int* slots, void* out, int T,
-                                    int H, int R, int r, float scale, cudaStream_t stream) {
+                                    int H, int R, int r, float scale, int window, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(R >= 1 && R <= 32 * LAT_MAXV, "latent_attention: a latent of %d values exceeds the kernel's limit of %d", R, 32 * LAT_MAXV);
   const size_t smem = (size_t)4 * (R + r) * sizeof(float);
@@ -165,7 +169,7 @@ extern "C" int tlc_latent_attention(const void* qa, const void* pages, int dtype
   dim3 grid(T, (H + 3) / 4);
   TLC_DISPATCH_DTYPE(dtype, TC, tlc_launch(latent_attention_warp_kernel<TC>, grid, dim3(128), smem, stream, (const TC*)qa,
                                            (const TC*)pages, sink, block_table, max_pages, positions, row_seq, slots, (TC*)out, H, R, r,
-                                           scale));
+                                           scale, window));
   TLC_CHECK_LAUNCH("latent_attention");
   return 0;
 }
@@ -265,7 +269,7 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bflo
                            const float* __restrict__ sink, const int* __restrict__ block_table, int max_pages,
                            const int* __restrict__ cu_seqlens, const int* __restrict__ slots, const int* __restrict__ start_pos,
                            __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int B, int H,
-                           int HP, int R, int r, float scale, int n_split, int n_tiles) {
+                           int HP, int R, int r, float scale, int n_split, int n_tiles, int window) {
   tlc_pdl(qa, pages, out, part_o, part_ml);
   constexpr int LTM = NWARP * 16, NT = NWARP * 32;
   extern __shared__ __align__(16) unsigned char lt_smem[];
@@ -293,9 +297,10 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bflo
   const int t0 = first + row0, p0 = start_pos[b] + row0;  // first packed row and its position
   const int h0 = hg * HP;
   const int n_kt_all = (p0 + rows - 1) / LT_KEYS + 1;     // key tiles the tile's last row sees
+  const int kt_lo = window > 0 ? max(0, p0 - window + 1) / LT_KEYS : 0;   // the first key tile the tile's first row sees
   const int split = blockIdx.y;
-  const int per = (n_kt_all + n_split - 1) / n_split;
-  const int kt0 = split * per, kt1 = min(n_kt_all, kt0 + per);
+  const int per = (n_kt_all - kt_lo + n_split - 1) / n_split;
+  const int kt0 = kt_lo + split * per, kt1 = min(n_kt_all, kt0 + per);
   const int* table = block_table + (size_t)slots[b] * max_pages;
   const uint32_t qs_u = (uint32_t)__cvta_generic_to_shared(qs), ks_u = (uint32_t)__cvta_generic_to_shared(ks);
   const int chunks_row = aw >> 3;
@@ -332,7 +337,8 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bflo
       for (int e = 0; e < 4; e++) o[i][j][e] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int ma = warp * 16 + g, mb = ma + 8;              // this thread's two pairs
-  const int pos_a = p0 + ma / HP, pos_b = p0 + mb / HP;   // their positions (keys 0..pos are visible)
+  const int pos_a = p0 + ma / HP, pos_b = p0 + mb / HP;   // their positions (keys 0..pos are visible, or the last `window`)
+  const int lo_a = window > 0 ? pos_a - window + 1 : 0, lo_b = window > 0 ? pos_b - window + 1 : 0;
   const float LOG2E = 1.4426950408889634f;
 
   for (int kt = kt0; kt < kt1; kt++) {
@@ -364,10 +370,10 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bflo
 #pragma unroll
     for (int j = 0; j < 8; j++) {
       const int k = key0 + 8 * j;
-      s[j][0] = k <= pos_a ? s[j][0] * scale : -INFINITY;
-      s[j][1] = k + 1 <= pos_a ? s[j][1] * scale : -INFINITY;
-      s[j][2] = k <= pos_b ? s[j][2] * scale : -INFINITY;
-      s[j][3] = k + 1 <= pos_b ? s[j][3] * scale : -INFINITY;
+      s[j][0] = (k <= pos_a && k >= lo_a) ? s[j][0] * scale : -INFINITY;
+      s[j][1] = (k + 1 <= pos_a && k + 1 >= lo_a) ? s[j][1] * scale : -INFINITY;
+      s[j][2] = (k <= pos_b && k >= lo_b) ? s[j][2] * scale : -INFINITY;
+      s[j][3] = (k + 1 <= pos_b && k + 1 >= lo_b) ? s[j][3] * scale : -INFINITY;
       mx_a = fmaxf(mx_a, fmaxf(s[j][0], s[j][1]));
       mx_b = fmaxf(mx_b, fmaxf(s[j][2], s[j][3]));
     }
@@ -441,7 +447,7 @@ latent_attention_tc_kernel(const __nv_bfloat16* __restrict__ qa, const __nv_bflo
             *reinterpret_cast<float2*>(po + i * 16 + j * 8 + 2 * q4) = make_float2(o[i][j][2 * e], o[i][j][2 * e + 1]);
         }
     } else {
-      const float sk = sink[h];
+      const float sk = sink ? sink[h] : -INFINITY;         // no sink: nothing joins the denominator
       const float mf = fmaxf(m_run[e], sk);
       const float w = exp2f((m_run[e] - mf) * LOG2E);
       const float inv = w / (l_run[e] * w + exp2f((sk - mf) * LOG2E));
@@ -465,7 +471,7 @@ latent_attention_merge_kernel(const float* __restrict__ part_o, const float* __r
   tlc_pdl(part_o, part_ml, out);
   __shared__ float wsh[64];
   const int th = blockIdx.x;
-  const float sk = sink[th % H];
+  const float sk = sink ? sink[th % H] : -INFINITY;
   const float* ml = part_ml + (size_t)th * n_split * 2;
   float mf = sk;
   for (int s = 0; s < n_split; s++) mf = fmaxf(mf, ml[2 * s]);
@@ -516,7 +522,7 @@ extern "C" int tlc_latent_attention_tc_splits(int n_tiles, int max_keys) {
 extern "C" int tlc_latent_attention_tc(const void* qa, const void* pages, const float* sink, const int* block_table, int max_pages,
                                        const int* cu_seqlens, const int* slots, const int* start_pos, void* out, float* part_o,
                                        float* part_ml, int B, int T, int tile_pairs, int n_tiles, int H, int R, int r, float scale,
-                                       int n_split, cudaStream_t stream) {
+                                       int n_split, int window, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(tlc_latent_attention_tc_ok(TLC_BF16, H, R, r), "latent_attention_tc: sizes H=%d R=%d r=%d are not built", H, R, r);
   TLC_REQUIRE(n_split >= 1 && n_split <= 64 && (n_split == 1 || (part_o && part_ml)), "latent_attention_tc: %d key ranges (1..64; more than one needs scratch)", n_split);
@@ -537,7 +543,7 @@ extern "C" int tlc_latent_attention_tc(const void* qa, const void* pages, const 
   typedef const __nv_bfloat16* BP;
 #define LT_LAUNCH(NV, NW)                                                                                                      \
   tlc_launch(latent_attention_tc_kernel<NV, NW>, grid, dim3(NW * 32), smem, stream, (BP)qa, (BP)pages, sink, block_table, max_pages, \
-             cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, part_o, part_ml, B, H, HP, R, r, scale, n_split, n_tiles)
+             cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, part_o, part_ml, B, H, HP, R, r, scale, n_split, n_tiles, window)
   if (tile_pairs == 128) { if (R <= 128) LT_LAUNCH(8, 8); else LT_LAUNCH(16, 8); }
   else { if (R <= 128) LT_LAUNCH(8, 4); else LT_LAUNCH(16, 4); }
 #undef LT_LAUNCH

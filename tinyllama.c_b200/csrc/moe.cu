@@ -21,12 +21,13 @@
 // lane finds the best of its experts (lane, lane + 32, ...) that come after the last choice in that order, and the
 // warp the best of the lanes.
 __global__ void __launch_bounds__(128)
-moe_topk_kernel(const float* __restrict__ logits, int ld, int T, int E, int top, int* __restrict__ ids, float* __restrict__ wts) {
+moe_topk_kernel(const float* __restrict__ logits, int ld, int T, int E, int top, int mode, int* __restrict__ ids,
+                float* __restrict__ wts) {
   tlc_pdl(logits, ids, wts);
   const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= T) return;
   const float* lr = logits + (size_t)t * ld;
-  float last = INFINITY;
+  float last = INFINITY, first = 0.f, sum = 0.f;
   int last_e = -1;
   for (int k = 0; k < top; k++) {
     float best = -INFINITY;
@@ -46,10 +47,21 @@ moe_topk_kernel(const float* __restrict__ logits, int ld, int T, int E, int top,
     if (be == 0x7fffffff) be = 0;            // (NaN logits: no order; keep indices valid)
     if (lane == 0) {
       ids[t * top + k] = be;
-      wts[t * top + k] = 1.0f / (1.0f + expf(-lr[be]));
+      if (mode == TLC_ROUTE_SOFTMAX) {       // the first choice has the largest logit: numerators exp(z_k - z_0)
+        if (k == 0) first = lr[be];
+        const float e = expf(lr[be] - first);
+        sum += e;
+        wts[t * top + k] = e;
+      } else {
+        wts[t * top + k] = 1.0f / (1.0f + expf(-lr[be]));
+      }
     }
     last = lr[be];
     last_e = be;
+  }
+  if (mode == TLC_ROUTE_SOFTMAX && lane == 0) {
+    const float inv = 1.0f / sum;
+    for (int k = 0; k < top; k++) wts[t * top + k] *= inv;
   }
 }
 
@@ -82,12 +94,13 @@ moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int E, int tm, int* __
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) order[atomicAdd(&cursor[ids[i]], 1)] = i;
 }
 
-extern "C" int tlc_moe_route(const float* logits, int ld, int T, int E, int top, int* ids, float* wts, int* order, int* offsets,
-                             int* tile_off, int tile_rows, cudaStream_t stream) {
+extern "C" int tlc_moe_route(const float* logits, int ld, int T, int E, int top, int mode, int* ids, float* wts, int* order,
+                             int* offsets, int* tile_off, int tile_rows, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(tile_rows >= 1, "moe_route: tiles of %d rows", tile_rows);
   TLC_REQUIRE(E >= 1 && top >= 1 && top <= E && E <= 4096, "moe_route: %d experts, %d chosen", E, top);
-  tlc_launch(moe_topk_kernel, dim3((T + 3) / 4), dim3(128), 0, stream, logits, ld, T, E, top, ids, wts);
+  TLC_REQUIRE(mode == TLC_ROUTE_SIGMOID || mode == TLC_ROUTE_SOFTMAX, "moe_route: unknown weighting %d", mode);
+  tlc_launch(moe_topk_kernel, dim3((T + 3) / 4), dim3(128), 0, stream, logits, ld, T, E, top, mode, ids, wts);
   TLC_CHECK_LAUNCH("moe_topk");
   tlc_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), stream, (const int*)ids, T * top, E, tile_rows, order,
              offsets, tile_off);
@@ -118,7 +131,7 @@ template <typename TA, typename TW, typename TO, bool QUICK>
 __global__ void __launch_bounds__(256)
 moe_gate_up_kernel(const TA* __restrict__ x, int ldx, const TW* __restrict__ wgu, const int* __restrict__ order,
                    const int* __restrict__ offsets, const int* __restrict__ tile_off, const float* __restrict__ wts, int E, int top,
-                   int F, int D, TO* __restrict__ act) {
+                   int F, int D, TO* __restrict__ act, int act_code, int w_out, float limit, float alpha) {
   tlc_pdl(x, order, offsets, tile_off, wts, act);
   __shared__ float As[MOE_TK][MOE_TM + 1], Gs[MOE_TK][MOE_TN + 1], Us[MOE_TK][MOE_TN + 1];
   __shared__ int tok[MOE_TM];
@@ -155,14 +168,14 @@ moe_gate_up_kernel(const TA* __restrict__ x, int ldx, const TW* __restrict__ wgu
   if (ty < rows) {
     const float w = wts[order[row0 + ty]];
     TO* o = act + (size_t)(row0 + ty) * F;
-    if (na < F) o[na] = from_f32<TO>(silu_of<QUICK>(w * g00) * (w * u00));
-    if (nb < F) o[nb] = from_f32<TO>(silu_of<QUICK>(w * g01) * (w * u01));
+    if (na < F) o[na] = from_f32<TO>(moe_pair_act<QUICK>(act_code, w_out, limit, alpha, w, g00, u00));
+    if (nb < F) o[nb] = from_f32<TO>(moe_pair_act<QUICK>(act_code, w_out, limit, alpha, w, g01, u01));
   }
   if (ty + 16 < rows) {
     const float w = wts[order[row0 + ty + 16]];
     TO* o = act + (size_t)(row0 + ty + 16) * F;
-    if (na < F) o[na] = from_f32<TO>(silu_of<QUICK>(w * g10) * (w * u10));
-    if (nb < F) o[nb] = from_f32<TO>(silu_of<QUICK>(w * g11) * (w * u11));
+    if (na < F) o[na] = from_f32<TO>(moe_pair_act<QUICK>(act_code, w_out, limit, alpha, w, g10, u10));
+    if (nb < F) o[nb] = from_f32<TO>(moe_pair_act<QUICK>(act_code, w_out, limit, alpha, w, g11, u11));
   }
 }
 
@@ -214,15 +227,17 @@ static inline int moe_max_tiles(int T, int E, int top) {
 
 extern "C" int tlc_moe_gate_up(const void* x, int x_dtype, int ldx, const void* wgu, int w_dtype, const int* order,
                                const int* offsets, const int* tile_off, const float* wts, int T, int E, int top, int F, int D,
-                               void* act, int act_dtype, cudaStream_t stream) {
+                               void* act, int act_dtype, int act_code, int w_out, float limit, float alpha, cudaStream_t stream) {
   if (T == 0) return 0;
+  TLC_REQUIRE(act_code >= TLC_ACT_SILU && act_code <= TLC_ACT_SWISH_CLAMPED, "moe_gate_up: unknown activation %d", act_code);
   dim3 grid(moe_max_tiles(T, E, top), (F + MOE_TN - 1) / MOE_TN);
   if (act_dtype == TLC_BF16) {
     TLC_DISPATCH_DTYPE(x_dtype, TA, TLC_DISPATCH_DTYPE(w_dtype, TW, tlc_launch(moe_gate_up_kernel<TA, TW, __nv_bfloat16, true>, grid,
-        dim3(256), 0, stream, (const TA*)x, ldx, (const TW*)wgu, order, offsets, tile_off, wts, E, top, F, D, (__nv_bfloat16*)act)));
+        dim3(256), 0, stream, (const TA*)x, ldx, (const TW*)wgu, order, offsets, tile_off, wts, E, top, F, D, (__nv_bfloat16*)act, act_code, w_out, limit,
+        alpha)));
   } else {
     TLC_DISPATCH_DTYPE(x_dtype, TA, TLC_DISPATCH_DTYPE(w_dtype, TW, tlc_launch(moe_gate_up_kernel<TA, TW, float, false>, grid,
-        dim3(256), 0, stream, (const TA*)x, ldx, (const TW*)wgu, order, offsets, tile_off, wts, E, top, F, D, (float*)act)));
+        dim3(256), 0, stream, (const TA*)x, ldx, (const TW*)wgu, order, offsets, tile_off, wts, E, top, F, D, (float*)act, act_code, w_out, limit, alpha)));
   }
   TLC_CHECK_LAUNCH("moe_gate_up");
   return 0;

@@ -1,0 +1,86 @@
+// What an attention mixer may do to its queries and keys between the input projection and the cache, and to its result
+// before the output projection.
+//
+// tlc_qk_rotate_norm works on the 32-bit projection in place, a warp per (row, head), query heads and key heads alike:
+// it turns the pairs of the first `rot` dimensions of a head by angle = position * inv_freq[i] (pairs (2i, 2i+1) with
+// interleaved != 0, else (i, i + rot/2); dimensions past `rot` pass unchanged) and then, with norm_eps >= 0, divides the
+// head by its root mean square over its `dim` dimensions, x / sqrt(mean(x^2) + eps), without a weight.  Heads may lie
+// `stride` >= dim values apart (a mixer whose values are wider than its keys pads the heads; the padding stays zero).
+// Everything is 32-bit; the kernels that store keys and values then need not rotate.
+//
+// tlc_gate_mul multiplies a [T, n] activation in place by sigmoid (or SiLU) of a column range of the 32-bit projection:
+// an output gate that reads the same input as the projections.
+#include "common.cuh"
+
+#define QK_MAXV 8     // a head of at most 32 * QK_MAXV dimensions
+
+__global__ void __launch_bounds__(128)
+qk_rotate_norm_kernel(float* __restrict__ qkv, int ld, int q_off, int k_off, int H, int KV, int stride, int dim,
+                      const float* __restrict__ inv_freq, int rot, int interleaved, float norm_eps,
+                      const int* __restrict__ positions, int T) {
+  tlc_pdl(qkv);
+  const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  const int units = H + KV;
+  if (w >= T * units) return;
+  const int t = w / units, u = w - t * units;
+  float* x = qkv + (size_t)t * ld + (u < H ? q_off + u * stride : k_off + (u - H) * stride);
+  const float fpos = (float)positions[t];
+  const int half = rot >> 1;
+  float ss = 0.f;
+  for (int p = lane; p < half; p += 32) {
+    const int ia = interleaved ? 2 * p : p, ib = interleaved ? 2 * p + 1 : p + half;
+    float sn, cs;
+    sincosf(fpos * inv_freq[p], &sn, &cs);
+    const float a = x[ia], b = x[ib];
+    const float ra = a * cs - b * sn, rb = b * cs + a * sn;
+    x[ia] = ra;
+    x[ib] = rb;
+    ss += ra * ra + rb * rb;
+  }
+  if (norm_eps < 0.f) return;
+  for (int d = rot + lane; d < dim; d += 32) { const float v = x[d]; ss += v * v; }
+  ss = warp_sum(ss);
+  const float s = 1.0f / sqrtf(ss / (float)dim + norm_eps);
+  __syncwarp();
+  for (int d = lane; d < dim; d += 32) x[d] *= s;
+}
+
+extern "C" int tlc_qk_rotate_norm(float* qkv, int ld, int q_off, int k_off, int H, int KV, int stride, int dim,
+                                  const float* inv_freq, int rot, int interleaved, float norm_eps, const int* positions, int T,
+                                  cudaStream_t stream) {
+  if (T == 0) return 0;
+  TLC_REQUIRE(dim >= 1 && dim <= stride && rot >= 0 && rot % 2 == 0 && rot <= dim, "qk_rotate_norm: %d rotated of %d dimensions, heads %d apart",
+              rot, dim, stride);
+  const long long warps = (long long)T * (H + KV);
+  tlc_launch(qk_rotate_norm_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, qkv, ld, q_off, k_off, H, KV, stride, dim,
+             inv_freq, rot, interleaved, norm_eps, positions, T);
+  TLC_CHECK_LAUNCH("qk_rotate_norm");
+  return 0;
+}
+
+template <typename TX, bool QUICK>
+__global__ void __launch_bounds__(256)
+gate_mul_kernel(TX* __restrict__ x, int ldx, const float* __restrict__ gate, int ldg, int n, int T, int act) {
+  tlc_pdl(x, gate);
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)T * n) return;
+  const int t = (int)(i / n), c = (int)(i - (long long)t * n);
+  const float g = gate[(size_t)t * ldg + c];
+  const float s = QUICK ? __fdividef(1.0f, 1.0f + __expf(-g)) : 1.0f / (1.0f + expf(-g));
+  TX* p = x + (size_t)t * ldx + c;
+  *p = from_f32<TX>(to_f32(*p) * (act == 1 ? g * s : s));
+}
+
+// x[t, c] *= sigmoid(gate[t, c]) (act 0) or silu(gate[t, c]) (act 1); x [T, n] of `dtype` with row stride ldx, gate float
+// with row stride ldg.
+extern "C" int tlc_gate_mul(void* x, int dtype, int ldx, const float* gate, int ldg, int n, int T, int act, cudaStream_t stream) {
+  if (T == 0 || n == 0) return 0;
+  TLC_REQUIRE(act == 0 || act == 1, "gate_mul: unknown gate %d", act);
+  const long long total = (long long)T * n;
+  const dim3 grid((unsigned)((total + 255) / 256));
+  if (dtype == TLC_BF16) tlc_launch(gate_mul_kernel<__nv_bfloat16, true>, grid, dim3(256), 0, stream, (__nv_bfloat16*)x, ldx, gate, ldg, n, T, act);
+  else if (dtype == TLC_F32) tlc_launch(gate_mul_kernel<float, false>, grid, dim3(256), 0, stream, (float*)x, ldx, gate, ldg, n, T, act);
+  else return tlc_fail(-1, "gate_mul: unknown dtype code %d", dtype);
+  TLC_CHECK_LAUNCH("gate_mul");
+  return 0;
+}

@@ -30,6 +30,9 @@
 #define TLC_PAGE 64
 #define TLC_ACT_SILU 0       /* activations of gated products: z * sigmoid(z) */
 #define TLC_ACT_GELU_TANH 1  /* 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) */
+#define TLC_ACT_SWISH_CLAMPED 2 /* experts only: g = min(g, limit), u = clamp(u, -limit, limit): g sigmoid(alpha g) (u + 1) */
+#define TLC_ROUTE_SIGMOID 0  /* a chosen expert's weight is the sigmoid of its logit */
+#define TLC_ROUTE_SOFTMAX 1  /* the chosen experts' weights are the softmax over their logits alone */
 
 #ifdef __cplusplus
 extern "C" {
@@ -65,8 +68,9 @@ int tlc_selftest_bounded_wait(cudaStream_t stream);
  * cache contents of earlier steps ahead of their own dependency wait. */
 int tlc_embed(const int* tokens, const void* table, int table_dtype, int T, int D, int V, float scale,
               float* out, cudaStream_t stream);
-/* out[r] = x[rows ? rows[r] : r] / sqrt(mean(x^2) + eps) * w;  x float [*, D], out [R, D] of out_dtype. */
-int tlc_rmsnorm(const float* x, const int* rows, const float* w, float eps, int R, int D, void* out,
+/* out[r] = x[rows ? rows[r] : r] / sqrt(mean(x^2) + eps) * w;  x float, rows of D values x_ld apart (a range of the
+ * columns of a wider matrix will do); out [R, D] of out_dtype. */
+int tlc_rmsnorm(const float* x, int x_ld, const int* rows, const float* w, float eps, int R, int D, void* out,
                 int out_dtype, cudaStream_t stream);
 /* Gate y (+ y2, where y2 is not NULL: an input that comes as two summands) by silu(z) and RMS-normalise per group,
  * in either order; w NULL: gate only.  out [T, Di] with row stride out_ld, multiplied by out_scale. */
@@ -227,20 +231,21 @@ int tlc_ssm_scan_ssd(const void* xbc, const float* dt, const float* A, const flo
 
 /* ---- attention over a shared latent (latent_attention.cu) -----------------------------------------------
  * A token's cache row is [c | kr] (R normed latent values, r rotated key values that all heads share); pages
- * [n_pages, TLC_PAGE, R + r].  tlc_latent_prepare reads a row's projections (float, row stride ld: H heads of
- * (dn | r) query values at q_off; R + r down-projected values at dkv_off, or dkv_off < 0 for a layer that reads
- * another layer's rows), writes the unrotated query parts to qn [T, H*dn], the rotated ones (interleaved pairs of the
+ * [n_pages, TLC_PAGE, R + r].  tlc_latent_prepare reads a row's projections (float: H heads of (dn | r) query values
+ * at q_off of qproj, row stride ldq; R + r down-projected values at dkv_off of proj, row stride ld, or dkv_off < 0 for
+ * a layer that reads another layer's rows; the two may be one buffer), writes the unrotated query parts to qn [T, H*dn], the rotated ones (interleaved pairs of the
  * first `rot` dimensions, angle = position * inv_freq[i]) into the last r columns of every head of qa [T, H*(R+r)],
  * and the row [rmsnorm(c) * cw | rotated kr] into its page.  qn, qa and pages are of `dtype`. */
-int tlc_latent_prepare(const float* proj, int ld, int q_off, int dkv_off, const float* cw, float eps,
+int tlc_latent_prepare(const float* qproj, int ldq, int q_off, const float* proj, int ld, int dkv_off, const float* cw, float eps,
                        const float* inv_freq, int rot, const int* positions, const int* row_seq, const int* slots,
                        const int* block_table, int max_pages, void* pages, void* qn, void* qa, int dtype, int T, int H,
                        int dn, int r, int R, cudaStream_t stream);
 /* out[t, h, :R] = sum_j p_j c_j over the keys 0..position of the row's sequence, p = softmax of (qa[t, h] . [c_j | kr_j])
- * * scale together with the head's sink (float [H]), which enters the maximum and the denominator only. */
+ * * scale together with the head's sink (float [H], or NULL for none), which enters the maximum and the denominator
+ * only.  window > 0: a row sees only the last `window` keys up to its own position. */
 int tlc_latent_attention(const void* qa, const void* pages, int dtype, const float* sink, const int* block_table,
                          int max_pages, const int* positions, const int* row_seq, const int* slots, void* out, int T,
-                         int H, int R, int r, float scale, cudaStream_t stream);
+                         int H, int R, int r, float scale, int window, cudaStream_t stream);
 /* The same on the tensor cores, for bfloat16 rows with R and R + r multiples of 16 and R <= 256 (tlc_..._ok): a block
  * takes tile_pairs (64 or 128) (row, head) pairs of one sequence and reads every page once, as keys and as values.  Rows of
  * a sequence are consecutive positions from start_pos.  n_tiles: an upper bound of the sum over sequences of
@@ -254,7 +259,7 @@ int tlc_latent_attention_tc_tile(int T, int B, int R, int r);      /* 64 or 128 
 int tlc_latent_attention_tc(const void* qa, const void* pages, const float* sink, const int* block_table, int max_pages,
                             const int* cu_seqlens, const int* slots, const int* start_pos, void* out, float* part_o,
                             float* part_ml, int B, int T, int tile_pairs, int n_tiles, int H, int R, int r, float scale,
-                            int n_split, cudaStream_t stream);
+                            int n_split, int window, cudaStream_t stream);
 /* A product per head: out[t, h, n] = sum_k a[t, h, k] w[h, n, k]; a with row stride lda and head stride a_hs, w
  * [H, N, K] dense, out with row stride ldo and head stride o_hs; 32-bit sums. */
 int tlc_linear_heads(const void* a, int a_dtype, int lda, int a_hs, const void* w, int w_dtype, void* out,
@@ -271,17 +276,43 @@ int tlc_mingru_scan(const float* proj, int ld, int z_off, int u_off, int g_off, 
                     int out_ld, const int* seg_start, const int* seq_seg_start, int n_seg, float* scratch,
                     cudaStream_t stream);
 
+/* ---- queries, keys and the output gate of an attention mixer (qk_transform.cu) ---------------------------
+ * tlc_qk_rotate_norm, in place on the float projection qkv [T, ld] (H query heads from q_off, KV key heads from k_off,
+ * heads `stride` values apart, `dim` <= stride of them in use): the pairs of the first `rot` dimensions turn by
+ * position * inv_freq[i] (pairs (2i, 2i+1) with interleaved != 0, else (i, i + rot/2)); then, with norm_eps >= 0, the
+ * head is divided by sqrt(mean over dim of x^2 + norm_eps).
+ * tlc_gate_mul: x[t, c] *= sigmoid(gate[t, c]) (act 0) or silu(gate[t, c]) (act 1); x [T, n] of `dtype`, row stride ldx;
+ * gate float, row stride ldg. */
+int tlc_qk_rotate_norm(float* qkv, int ld, int q_off, int k_off, int H, int KV, int stride, int dim, const float* inv_freq,
+                       int rot, int interleaved, float norm_eps, const int* positions, int T, cudaStream_t stream);
+int tlc_gate_mul(void* x, int dtype, int ldx, const float* gate, int ldg, int n, int T, int act, cudaStream_t stream);
+
+/* ---- gated delta rule (delta_rule.cu) -------------------------------------------------------------------
+ * Per head: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with S [dk, dv] float per (slot, head) in state
+ * [n_slots, H, dk, dv] (zero at position 0).  tlc_delta_prepare normalises, in place in qkv [T, ld] float, the G query
+ * heads at q_off (x / sqrt(sum x^2 + l2_eps) * q_scale) and the G key heads at k_off (the same without the scale), and
+ * writes beta[t, h] = sigmoid(proj[t, b_off + h]).  tlc_delta_rule walks every sequence's rows: values (H heads of dv) at
+ * v_off, beta and decay float [T, H]; y [T, ldy] float receives o (head h at column h * dv). */
+int tlc_delta_prepare(float* qkv, int ld, int q_off, int k_off, int G, int dk, float l2_eps, float q_scale, const float* proj,
+                      int ldp, int b_off, int H, float* beta, int T, cudaStream_t stream);
+int tlc_delta_rule(const float* qkv, int ld, int q_off, int k_off, int v_off, const float* beta, const float* decay,
+                   float* state, const int* cu_seqlens, const int* slots, const int* start_pos, int B, int H, int G, int dk,
+                   int dv, float* y, int ldy, cudaStream_t stream);
+
 /* ---- mixture of experts (moe.cu) ------------------------------------------------------------------------
  * tlc_moe_route: logits float [T, ld] (E columns) -> per token its `top` experts by descending logit (lowest index
- * first on ties) in ids [T*top] with weights wts = sigmoid(logit); order [T*top] lists the pairs (t * top + k) sorted
+ * first on ties) in ids [T*top] with weights wts = sigmoid(logit) (mode TLC_ROUTE_SIGMOID) or the softmax over the
+ * chosen logits (TLC_ROUTE_SOFTMAX); order [T*top] lists the pairs (t * top + k) sorted
  * by expert, offsets [E+1] every expert's first sorted position, tile_off [E+1] its first tile of tile_rows sorted rows
  * (32 for tlc_moe_gate_up / tlc_moe_down; 32 or 64 for tlc_moe_experts_mma, which is told the same number). */
-int tlc_moe_route(const float* logits, int ld, int T, int E, int top, int* ids, float* wts, int* order, int* offsets,
+int tlc_moe_route(const float* logits, int ld, int T, int E, int top, int mode, int* ids, float* wts, int* order, int* offsets,
                   int* tile_off, int tile_rows, cudaStream_t stream);
-/* act[i, :F] = silu(w g) * (w u) for sorted position i: g | u = wgu[e] x[token], wgu [E, 2F, D], w the pair's weight. */
+/* act[i, :F] for sorted position i from g | u = wgu[e] x[token], wgu [E, 2F, D], and the pair's weight w: with w_out 0
+ * the weight scales the expert's input, act(w g) * (w u); with w_out 1 its output, w * act(g, u).  act: TLC_ACT_SILU,
+ * TLC_ACT_GELU_TANH, or TLC_ACT_SWISH_CLAMPED with its limit and alpha. */
 int tlc_moe_gate_up(const void* x, int x_dtype, int ldx, const void* wgu, int w_dtype, const int* order,
                     const int* offsets, const int* tile_off, const float* wts, int T, int E, int top, int F, int D,
-                    void* act, int act_dtype, cudaStream_t stream);
+                    void* act, int act_dtype, int act_code, int w_out, float limit, float alpha, cudaStream_t stream);
 /* y[pair, :D] = wd[e] act[i, :] for sorted position i of pair (t, k); wd [E, D, F]; y float [T*top, D]. */
 int tlc_moe_down(const void* act, int act_dtype, const void* wd, int w_dtype, const int* order, const int* offsets,
                  const int* tile_off, int T, int E, int top, int F, int D, float* y, cudaStream_t stream);
@@ -295,7 +326,7 @@ int tlc_linear_heads_mma(const void* a, int lda, int a_hs, const void* w, void* 
                          int T, int H, int N, int K, cudaStream_t stream);
 int tlc_moe_experts_mma(const void* x, int ldx, const void* wgu, const void* wd, const int* order, const int* offsets,
                         const int* tile_off, const float* wts, int T, int E, int top, int F, int D, void* act, float* y,
-                        int tile_rows, cudaStream_t stream);
+                        int tile_rows, int act_code, int w_out, float limit, float alpha, cudaStream_t stream);
 
 /* ---- sampling (sampling.cu) ------------------------------------------------------------------------ */
 /* out[r] = first index of the maximum of logits[r].  work: NULL (one block a row), or 12 * R bytes, 8-byte

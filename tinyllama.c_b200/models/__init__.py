@@ -1,3 +1,4 @@
 from .model import Model  # noqa: F401
 from . import falcon_h1  # noqa: F401  (registers FalconH1ForCausalLM)
 from . import turevik  # noqa: F401  (registers Turevik)
+from . import porarax  # noqa: F401  (registers Porarax)

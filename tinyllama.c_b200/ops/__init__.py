@@ -41,7 +41,7 @@ _SIGNATURES = {
     "tlc_wait_limit_cycles": (_i, [_ll]),
     "tlc_selftest_bounded_wait": (_i, [_vp]),
     "tlc_embed": (_i, [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp]),
-    "tlc_rmsnorm": (_i, [_vp, _vp, _vp, _f, _i, _i, _vp, _i, _vp]),
+    "tlc_rmsnorm": (_i, [_vp, _i, _vp, _vp, _f, _i, _i, _vp, _i, _vp]),
     "tlc_gated_rmsnorm": (_i, [_vp, _vp, _vp, _i, _i, _vp, _f, _i, _i, _i, _i, _vp, _i, _i, _f, _vp]),
     "tlc_swiglu": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _i, _vp]),
     "tlc_gather_rows": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
@@ -94,20 +94,25 @@ _SIGNATURES = {
     "tlc_glu": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp]),
     "tlc_rmsnorm_shift": (_i, [_vp, _vp, _vp, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "tlc_rmsnorm_add": (_i, [_vp, _i, _vp, _vp, _i, _i, _vp, _f, _i, _i, _vp, _i, _vp]),
-    "tlc_latent_prepare": (_i, [_vp, _i, _i, _i, _vp, _f, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                _vp]),
-    "tlc_latent_attention": (_i, [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
+    "tlc_latent_prepare": (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _f, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i,
+                                _i, _i, _vp]),
+    "tlc_latent_attention": (_i, [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp]),
     "tlc_latent_attention_tc_ok": (_i, [_i, _i, _i, _i]),
     "tlc_latent_attention_tc_splits": (_i, [_i, _i]),
     "tlc_latent_attention_tc_tile": (_i, [_i, _i, _i, _i]),
-    "tlc_latent_attention_tc": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
+    "tlc_latent_attention_tc": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i,
+                                     _vp]),
     "tlc_linear_heads": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "tlc_grouped_mma_ok": (_i, [_i, _i, _vp, _i, _i, _vp, _i]),
     "tlc_linear_heads_mma": (_i, [_vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
-    "tlc_moe_experts_mma": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp]),
+    "tlc_moe_experts_mma": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _i, _i, _f, _f, _vp]),
     "tlc_mingru_scan": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _vp, _vp]),
-    "tlc_moe_route": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
-    "tlc_moe_gate_up": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp]),
+    "tlc_moe_route": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "tlc_moe_gate_up": (_i, [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _i, _i, _f, _f, _vp]),
+    "tlc_qk_rotate_norm": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _f, _vp, _i, _vp]),
+    "tlc_gate_mul": (_i, [_vp, _i, _i, _vp, _i, _i, _i, _i, _vp]),
+    "tlc_delta_prepare": (_i, [_vp, _i, _i, _i, _i, _i, _f, _f, _vp, _i, _i, _i, _vp, _i, _vp]),
+    "tlc_delta_rule": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp]),
     "tlc_moe_down": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
     "tlc_argmax": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "tlc_sample": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _f, _f, _f, _i, _f, _f, _vp, _vp]),
@@ -244,12 +249,14 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, scale: float, out: torch.Te
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
             rows: Optional[torch.Tensor] = None) -> None:
-    """out[r] = rmsnorm(x[rows[r]] or x[r]) * weight; x float32 [*, D]."""
+    """out[r] = rmsnorm(x[rows[r]] or x[r]) * weight; x float32 [*, D] with dense rows (a range of the columns of a
+    wider matrix will do)."""
     _gpu(x, weight, out, rows)
     D = x.shape[1]
     R = out.shape[0]
-    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous() or out.shape[1] != D:
-        raise KernelError("rmsnorm: x must be contiguous float32 and out contiguous [R, D]")
+    if x.dtype != torch.float32 or not out.is_contiguous() or out.shape[1] != D:
+        raise KernelError("rmsnorm: x must be float32 and out contiguous [R, D]")
+    x_ld = _rows(x, "rmsnorm input")
     _f32vec(weight, D, "rmsnorm weight")
     if rows is not None:
         _i32(rows, "rmsnorm rows")
@@ -257,7 +264,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
             raise KernelError("rmsnorm: one row index per output row")
     elif x.shape[0] != R:
         raise KernelError("rmsnorm: x and out differ in rows")
-    _call("tlc_rmsnorm", x.data_ptr(), _p(rows), weight.data_ptr(), float(eps), R, D, out.data_ptr(),
+    _call("tlc_rmsnorm", x.data_ptr(), x_ld, _p(rows), weight.data_ptr(), float(eps), R, D, out.data_ptr(),
           dtype_code(out.dtype), _stream())
 
 
@@ -820,19 +827,26 @@ def sample(logits: torch.Tensor, work: torch.Tensor, history: Optional[torch.Ten
 MAX_LATENT = 512          # latent_attention.cu: 32 * LAT_MAXV values of a latent
 
 
-def latent_prepare(proj: torch.Tensor, q_off: int, dkv_off: Optional[int], norm_weight: Optional[torch.Tensor], eps: float,
+def latent_prepare(proj: Optional[torch.Tensor], q_off: int, dkv_off: Optional[int], norm_weight: Optional[torch.Tensor], eps: float,
                    inv_freq: torch.Tensor, step, block_table: torch.Tensor, pages: torch.Tensor, qn: torch.Tensor,
-                   qa: torch.Tensor, H: int, dn: int, r: int, R: int) -> None:
+                   qa: torch.Tensor, H: int, dn: int, r: int, R: int, q_proj: Optional[torch.Tensor] = None) -> None:
     """From a row's projections (float32 [T, *]: H heads of (dn | r) query values at q_off, R + r down-projected values
-    at dkv_off, None for a layer that reads another layer's rows): the unrotated query parts to qn [T, H*dn], the
+    at dkv_off, None for a layer that reads another layer's rows; q_proj: the buffer that holds the queries, where it
+    is not proj itself, which may then be None with dkv_off None): the unrotated query parts to qn [T, H*dn], the
     rotated ones into the last r columns of every head of qa [T, H*(R+r)], and the cache row [rmsnorm(c) * norm_weight
     | rotated kr] into its page of pages [n, 64, R+r].  The rotation turns interleaved pairs of the first
     2 * len(inv_freq) dimensions."""
-    _gpu(proj, norm_weight, inv_freq, block_table, pages, qn, qa)
-    T = proj.shape[0]
+    if q_proj is None:
+        q_proj = proj
+    if proj is None:
+        if dkv_off is not None:
+            raise KernelError("latent_prepare: a down-projection's columns without its buffer")
+        proj = q_proj
+    _gpu(proj, q_proj, norm_weight, inv_freq, block_table, pages, qn, qa)
+    T = q_proj.shape[0]
     _i32(block_table, "block_table")
-    if proj.dtype != torch.float32:
-        raise KernelError("latent_prepare: float32 projections")
+    if proj.dtype != torch.float32 or q_proj.dtype != torch.float32 or proj.shape[0] != T:
+        raise KernelError("latent_prepare: float32 projections of equal rows")
     if qn.dtype != pages.dtype or qa.dtype != pages.dtype or not qn.is_contiguous() or not qa.is_contiguous() \
             or tuple(qn.shape) != (T, H * dn) or tuple(qa.shape) != (T, H * (R + r)):
         raise KernelError("latent_prepare: qn [T, H*dn] and qa [T, H*(R+r)] must be contiguous and of the pages' type")
@@ -841,7 +855,8 @@ def latent_prepare(proj: torch.Tensor, q_off: int, dkv_off: Optional[int], norm_
     if dkv_off is not None:
         _f32vec(norm_weight, R, "latent norm weight")
     _f32vec(inv_freq, inv_freq.numel(), "rotation inv_freq")
-    _call("tlc_latent_prepare", proj.data_ptr(), _rows(proj, "proj"), int(q_off), -1 if dkv_off is None else int(dkv_off),
+    _call("tlc_latent_prepare", q_proj.data_ptr(), _rows(q_proj, "q_proj"), int(q_off), proj.data_ptr(), _rows(proj, "proj"),
+          -1 if dkv_off is None else int(dkv_off),
           _p(norm_weight), float(eps), inv_freq.data_ptr(), 2 * inv_freq.numel(), step.positions.data_ptr(),
           step.row_seq.data_ptr(), step.slots.data_ptr(), block_table.data_ptr(), block_table.shape[1], pages.data_ptr(),
           qn.data_ptr(), qa.data_ptr(), dtype_code(pages.dtype), T, H, dn, r, R, _stream())
@@ -857,10 +872,10 @@ def latent_attention_tc(on: bool) -> None:
     _latent_tc = bool(on)
 
 
-def latent_attention(qa: torch.Tensor, pages: torch.Tensor, sink: torch.Tensor, block_table: torch.Tensor, step,
-                     out: torch.Tensor, H: int, R: int, r: int, scale: float, key_ranges: int = 0) -> None:
-    """out [T, H*R]: every head's softmax-weighted sum of the latents of keys 0..position, scores (qa . [c | kr]) * scale,
-    with the head's sink in the denominator.  bfloat16 rows of sizes the tensor-core kernel is built for take it (all
+def latent_attention(qa: torch.Tensor, pages: torch.Tensor, sink: Optional[torch.Tensor], block_table: torch.Tensor, step,
+                     out: torch.Tensor, H: int, R: int, r: int, scale: float, key_ranges: int = 0, window: int = 0) -> None:
+    """out [T, H*R]: every head's softmax-weighted sum of the latents of keys 0..position (with window > 0: of the last
+    `window` of them), scores (qa . [c | kr]) * scale, with the head's sink (None: no sink) in the denominator.  bfloat16 rows of sizes the tensor-core kernel is built for take it (all
     heads of a row share every page read); key_ranges > 0 fixes into how many ranges it cuts a tile's keys (0: chosen:
     more than one for few rows over many keys)."""
     _gpu(qa, pages, sink, block_table, out)
@@ -878,19 +893,20 @@ def latent_attention(qa: torch.Tensor, pages: torch.Tensor, sink: torch.Tensor, 
         B = step.n_seqs
         pairs = lib.tlc_latent_attention_tc_tile(T, B, R, r)          # (row, head) pairs a tile: 128 for prompts, else 64
         n_tiles = T // (pairs // hp) + B
-        n_split = min(64, key_ranges) if key_ranges > 0 else lib.tlc_latent_attention_tc_splits(n_tiles * ((H + hp - 1) // hp),
-                                                                                                  int(step.max_context))
+        seen = int(step.max_context) if not window else min(int(step.max_context), int(window) + pairs // hp)   # keys a tile sees
+        n_split = min(64, key_ranges) if key_ranges > 0 else lib.tlc_latent_attention_tc_splits(n_tiles * ((H + hp - 1) // hp), seen)
         part_o = part_ml = None
         if n_split > 1:
             part_o = torch.empty((T, H, n_split, R), dtype=torch.float32, device=qa.device)
             part_ml = torch.empty((T, H, n_split, 2), dtype=torch.float32, device=qa.device)
-        _call("tlc_latent_attention_tc", qa.data_ptr(), pages.data_ptr(), sink.data_ptr(), block_table.data_ptr(),
+        _call("tlc_latent_attention_tc", qa.data_ptr(), pages.data_ptr(), _p(sink), block_table.data_ptr(),
               block_table.shape[1], step.cu_seqlens.data_ptr(), step.slots.data_ptr(), step.start_pos.data_ptr(),
-              out.data_ptr(), _p(part_o), _p(part_ml), B, T, pairs, n_tiles, H, R, r, float(scale), int(n_split), _stream())
+              out.data_ptr(), _p(part_o), _p(part_ml), B, T, pairs, n_tiles, H, R, r, float(scale), int(n_split), int(window or 0),
+              _stream())
         return
-    _call("tlc_latent_attention", qa.data_ptr(), pages.data_ptr(), dtype_code(pages.dtype), sink.data_ptr(),
+    _call("tlc_latent_attention", qa.data_ptr(), pages.data_ptr(), dtype_code(pages.dtype), _p(sink),
           block_table.data_ptr(), block_table.shape[1], step.positions.data_ptr(), step.row_seq.data_ptr(),
-          step.slots.data_ptr(), out.data_ptr(), T, H, R, r, float(scale), _stream())
+          step.slots.data_ptr(), out.data_ptr(), T, H, R, r, float(scale), int(window or 0), _stream())
 
 
 _grouped_mma = not bool(int(os.environ.get("TLC_DISABLE_GROUPED_MMA", "0")))
@@ -960,10 +976,16 @@ def moe_tile_rows(x: torch.Tensor, w_gate_up: torch.Tensor, act_dtype: torch.dty
     return 64 if _moe_mma_ok(x, w_gate_up, act_dtype) and x.shape[0] * top >= 64 * E else 32
 
 
-def moe_route(logits: torch.Tensor, n_experts: int, top: int, tile_rows: int = 32):
+ROUTE_WEIGHTS = {"sigmoid": 0, "softmax": 1}
+MOE_ACTS = dict(GLU_ACTS, swish_clamped=2)
+
+
+def moe_route(logits: torch.Tensor, n_experts: int, top: int, tile_rows: int = 32, weights: str = "sigmoid"):
     """Routing of every row of logits (float32 [T, >= E], the first E columns): returns (ids [T*top] int32, weights
-    [T*top] float32 = sigmoid of the chosen logits, order [T*top], offsets [E+1], tile_off [E+1], tile_rows) as
-    tlc_moe_route describes them."""
+    [T*top] float32 = sigmoid of the chosen logits, or with weights "softmax" the softmax over the chosen logits alone,
+    order [T*top], offsets [E+1], tile_off [E+1], tile_rows) as tlc_moe_route describes them."""
+    if weights not in ROUTE_WEIGHTS:
+        raise KernelError(f"moe_route: unknown weighting '{weights}'; known: {sorted(ROUTE_WEIGHTS)}")
     _gpu(logits)
     T = logits.shape[0]
     if logits.dtype != torch.float32 or logits.shape[1] < n_experts:
@@ -976,15 +998,21 @@ def moe_route(logits: torch.Tensor, n_experts: int, top: int, tile_rows: int = 3
     wts = torch.empty(T * top, dtype=torch.float32, device=dev)
     global _launches
     _launches += 1                      # (two kernels)
-    _call("tlc_moe_route", logits.data_ptr(), _rows(logits, "router logits"), T, int(n_experts), int(top), ids.data_ptr(),
+    _call("tlc_moe_route", logits.data_ptr(), _rows(logits, "router logits"), T, int(n_experts), int(top), ROUTE_WEIGHTS[weights],
+          ids.data_ptr(),
           wts.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_off.data_ptr(), int(tile_rows), _stream())
     return ids, wts, order, offsets, tile_off, int(tile_rows)
 
 
 def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, routing, top: int, act: torch.Tensor,
-                y: torch.Tensor) -> None:
-    """y[t, k, :] = expert_k(weight * x[t]) for every chosen (token, expert) pair: w_gate_up [E, 2F, D], w_down
-    [E, D, F]; act [T*top, F] is scratch of the activation type, y float32 [T, top, D]."""
+                y: torch.Tensor, act_fn: str = "silu", weight_on: str = "input", limit: float = 0.0, alpha: float = 1.0) -> None:
+    """y[t, k, :] for every chosen (token, expert) pair: expert_k(weight * x[t]) with weight_on "input", weight *
+    expert_k(x[t]) with "output"; w_gate_up [E, 2F, D], w_down [E, D, F]; act [T*top, F] is scratch of the activation
+    type, y float32 [T, top, D].  act_fn: "silu" / "gelu_tanh" (act(g) * u), or "swish_clamped": with g = min(g, limit)
+    and u held within +-limit, g * sigmoid(alpha * g) * (u + 1)."""
+    if act_fn not in MOE_ACTS or weight_on not in ("input", "output"):
+        raise KernelError(f"moe_experts: unknown activation '{act_fn}' or weight placement '{weight_on}'")
+    code, w_out = MOE_ACTS[act_fn], int(weight_on == "output")
     _gpu(x, w_gate_up, w_down, act, y)
     ids, wts, order, offsets, tile_off, tile_rows = routing
     T, D = x.shape
@@ -999,12 +1027,86 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     ldx = _rows(x, "moe input")
     if _moe_mma_ok(x, w_gate_up, act.dtype):
         _call("tlc_moe_experts_mma", x.data_ptr(), ldx, w_gate_up.data_ptr(), w_down.data_ptr(), order.data_ptr(), offsets.data_ptr(),
-              tile_off.data_ptr(), wts.data_ptr(), T, E, int(top), F, D, act.data_ptr(), y.data_ptr(), tile_rows, _stream())
+              tile_off.data_ptr(), wts.data_ptr(), T, E, int(top), F, D, act.data_ptr(), y.data_ptr(), tile_rows, code, w_out,
+              float(limit), float(alpha), _stream())
         return
     if tile_rows != 32:
         raise KernelError("moe_experts: the CUDA-core products take a routing made for tiles of 32 rows")
     _call("tlc_moe_gate_up", x.data_ptr(), dtype_code(x.dtype), _rows(x, "moe input"), w_gate_up.data_ptr(),
           dtype_code(w_gate_up.dtype), order.data_ptr(), offsets.data_ptr(), tile_off.data_ptr(), wts.data_ptr(), T, E, int(top),
-          F, D, act.data_ptr(), dtype_code(act.dtype), _stream())
+          F, D, act.data_ptr(), dtype_code(act.dtype), code, w_out, float(limit), float(alpha), _stream())
     _call("tlc_moe_down", act.data_ptr(), dtype_code(act.dtype), w_down.data_ptr(), dtype_code(w_down.dtype), order.data_ptr(),
           offsets.data_ptr(), tile_off.data_ptr(), T, E, int(top), F, D, y.data_ptr(), _stream())
+
+
+# ---- queries, keys and output gate of an attention mixer ---------------------------------------------------
+def qk_rotate_norm(qkv: torch.Tensor, q_off: int, k_off: int, H: int, KV: int, stride: int, dim: int, inv_freq: torch.Tensor,
+                   interleaved: bool, norm_eps: Optional[float], positions: torch.Tensor) -> None:
+    """In place on the float32 projection qkv [T, *] (H query heads from column q_off, KV key heads from k_off, heads
+    `stride` values apart of which `dim` are in use): turns the pairs of the first 2 * len(inv_freq) dimensions of every
+    head by position * inv_freq[i] (neighbours (2i, 2i+1) when interleaved, else (i, i + half)), then, with norm_eps not
+    None, divides the head by sqrt(mean(x^2) + norm_eps)."""
+    _gpu(qkv, inv_freq, positions)
+    T = qkv.shape[0]
+    _i32(positions, "positions")
+    _f32vec(inv_freq, inv_freq.numel(), "rotation inv_freq")
+    ld = _rows(qkv, "qkv")
+    if qkv.dtype != torch.float32 or max(q_off + H * stride, k_off + KV * stride) > max(ld, qkv.shape[1]):
+        raise KernelError("qk_rotate_norm: a float32 projection that holds every head")
+    _call("tlc_qk_rotate_norm", qkv.data_ptr(), ld, int(q_off), int(k_off), int(H), int(KV), int(stride), int(dim),
+          inv_freq.data_ptr(), 2 * inv_freq.numel(), int(bool(interleaved)), -1.0 if norm_eps is None else float(norm_eps),
+          positions.data_ptr(), T, _stream())
+
+
+GATES = {"sigmoid": 0, "silu": 1}
+
+
+def gate_mul(x: torch.Tensor, gate: torch.Tensor, kind: str = "sigmoid") -> None:
+    """x[t, c] *= sigmoid(gate[t, c]) (or silu); x [T, n] with dense rows, gate float32 [T, n] (a range of the columns of
+    a wider projection will do)."""
+    _gpu(x, gate)
+    if kind not in GATES:
+        raise KernelError(f"gate_mul: unknown gate '{kind}'; known: {sorted(GATES)}")
+    T, n = x.shape
+    if gate.dtype != torch.float32 or tuple(gate.shape) != (T, n):
+        raise KernelError("gate_mul: the gate must be float32 of x's shape")
+    _call("tlc_gate_mul", x.data_ptr(), dtype_code(x.dtype), _rows(x, "gate_mul x"), gate.data_ptr(), _rows(gate, "gate"), n, T,
+          GATES[kind], _stream())
+
+
+# ---- gated delta rule ---------------------------------------------------------------------------------------
+MAX_DELTA_KEY_DIM = 256   # delta_rule.cu: rows of a head's state that the threads of a column hold in registers
+
+
+def delta_prepare(qkv: torch.Tensor, q_off: int, k_off: int, G: int, dk: int, l2_eps: float, q_scale: float, proj: torch.Tensor,
+                  b_off: int, H: int, beta: torch.Tensor) -> None:
+    """In place on qkv (float32 [T, *], G query heads of dk values from q_off, G key heads from k_off): every head becomes
+    x / sqrt(sum(x^2) + l2_eps), the queries also times q_scale; beta [T, H] float32 = sigmoid(proj[:, b_off : b_off + H])."""
+    _gpu(qkv, proj, beta)
+    T = qkv.shape[0]
+    if qkv.dtype != torch.float32 or proj.dtype != torch.float32 or beta.dtype != torch.float32 or not beta.is_contiguous() \
+            or tuple(beta.shape) != (T, H) or proj.shape[0] != T:
+        raise KernelError("delta_prepare: float32 tensors, beta contiguous [T, H]")
+    _call("tlc_delta_prepare", qkv.data_ptr(), _rows(qkv, "qkv"), int(q_off), int(k_off), int(G), int(dk), float(l2_eps),
+          float(q_scale), proj.data_ptr(), _rows(proj, "proj"), int(b_off), int(H), beta.data_ptr(), T, _stream())
+
+
+def delta_rule(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, beta: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
+               step, y: torch.Tensor, H: int, G: int, dk: int, dv: int) -> None:
+    """The gated delta rule over every sequence's rows of the step, from its slot's state [n_slots, H, dk, dv] float32
+    (zero at position 0; updated in place): S <- g S; u = beta (v - S^T k); S <- S + k u^T; y = S^T q.  qkv float32
+    [T, *] holds the prepared queries and keys (G heads of dk) and the values (H heads of dv); beta, decay float32 [T, H];
+    y float32 [T, H*dv]."""
+    _gpu(qkv, beta, decay, state, y)
+    T = qkv.shape[0]
+    for t, n in ((beta, "beta"), (decay, "decay")):
+        if t.dtype != torch.float32 or not t.is_contiguous() or tuple(t.shape) != (T, H):
+            raise KernelError(f"delta_rule: {n} must be contiguous float32 [T, H]")
+    if qkv.dtype != torch.float32 or state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (H, dk, dv):
+        raise KernelError("delta_rule: float32 inputs and a contiguous float32 state [n_slots, H, dk, dv]")
+    if y.dtype != torch.float32:
+        raise KernelError("delta_rule: y must be float32")
+    ldy = _out_rows(y, T, H * dv, "delta_rule")
+    _call("tlc_delta_rule", qkv.data_ptr(), _rows(qkv, "qkv"), int(q_off), int(k_off), int(v_off), beta.data_ptr(), decay.data_ptr(),
+          state.data_ptr(), step.cu_seqlens.data_ptr(), step.slots.data_ptr(), step.start_pos.data_ptr(), step.n_seqs, int(H), int(G),
+          int(dk), int(dv), y.data_ptr(), ldy, _stream())

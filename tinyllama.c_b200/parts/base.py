@@ -201,7 +201,8 @@ class LayerSpec:
     """One layer as data: pre-mixer norm, mixers that run in parallel on the normed input and
     add into the residual stream, pre-feed-forward norm, feed-forward.  With an output norm a sublayer's result is
     normed before it is added: x <- x + out_norm(sublayer(norm(x))).  A norm part that keeps per-sequence state (a token
-    shift) declares it like a mixer does."""
+    shift) declares it like a mixer does.  A feed-forward without a norm of its own (ffn_norm None) runs in parallel with
+    the mixers: it reads what the mixers read, h = mixer_norm(x), and x <- x + mixers(h) + ffn(h)."""
     mixer_norm: PartSpec
     mixers: Tuple[PartSpec, ...]
     ffn_norm: Optional[PartSpec]

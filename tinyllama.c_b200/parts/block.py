@@ -1,5 +1,6 @@
 """A layer: norm -> mixers in parallel on the same normed input -> residual; norm ->
-feed-forward -> residual.  With output norms (LayerSpec.mixer_out_norm, ffn_out_norm) a sublayer's
+feed-forward -> residual.  A feed-forward without a norm of its own reads the mixers' normed input
+and is one more parallel summand.  With output norms (LayerSpec.mixer_out_norm, ffn_out_norm) a sublayer's
 result is collected in a 32-bit buffer of its own, normed, and then added.
 
 CodeClaper/tinyllama.c falcon_h1.c:311-395: n = norm(x); x = (x + attn(n)) + ssm(n);
@@ -65,6 +66,11 @@ class Block(Part):
         self.ffn = spec.ffn.build() if spec.ffn is not None else None
         self.mixer_out_norm = spec.mixer_out_norm.build() if spec.mixer_out_norm is not None else None
         self.ffn_out_norm = spec.ffn_out_norm.build() if spec.ffn_out_norm is not None else None
+        # a feed-forward without a norm of its own is a parallel branch: it reads the mixers' normed input
+        self.parallel_ffn = self.ffn is not None and self.ffn_norm is None
+        if self.parallel_ffn and (not self.mixers or self.ffn_out_norm is not None or self.mixer_out_norm is not None):
+            raise ValueError("a feed-forward without a norm of its own runs beside the mixers on their normed input: the layer "
+                             "needs mixers and takes no output norms")
         self.dtype: Optional[torch.dtype] = None
         # a part whose forward() takes `accumulate` can overwrite its target instead of adding into it
         takes = lambda p: p is not None and "accumulate" in inspect.signature(p.forward).parameters
@@ -231,7 +237,10 @@ class Block(Part):
             else:
                 for m in self.mixers:
                     m.forward(normed, step, cache, x32)
-        if self.ffn is not None:
+        if self.parallel_ffn:
+            # h was normed before the mixers added anything; the sum x + mixers(h) + ffn(h) forms in the residual stream
+            self.ffn.forward(normed, x32)
+        elif self.ffn is not None:
             normed = self._pre_norm(self.ffn_norm, x32, "block.ffn_normed", step, cache)
             if self.ffn_out_norm is None:
                 self.ffn.forward(normed, x32)

@@ -73,7 +73,7 @@ class SwiGLU(Part):
 
 @register_feed_forward("moe")
 class MoEFeedForward(Part):
-    """Mixture of experts with a sigmoid router.
+    """Mixture of experts.  By default, with a sigmoid router:
 
     Router scores s = sigmoid(W_router h), the logits as 32-bit sums; a token is routed to its `top` highest-scoring experts, and
     its weights are those scores unchanged (they need not sum to one).  An expert is fed the token scaled by its weight: the result
@@ -84,11 +84,24 @@ class MoEFeedForward(Part):
 
     The experts' weights are stacked [E, 2F, D] and [E, D, F]; rows are sorted by expert on the device, and every
     (token, choice) pair's result gets a row of its own, which the norm that follows (or `forward`) adds in the order
-    of the token's choices: a token's result does not depend on what else is in the batch."""
+    of the token's choices: a token's result does not depend on what else is in the batch.
+
+    Other routers and experts, by constructor arguments: a bias on the router's logits (router_bias_name); weights that are
+    the softmax over the chosen logits alone (weights="softmax"); the weight applied to what the expert returns instead of
+    to what it is fed (weight_on="output": sum_e s_e expert_e(h); the down product is linear, so the weight multiplies the
+    32-bit activation); the activation act="swish_clamped": with g = min(W_gate h, limit) and u = W_up h held within
+    +-limit, g * sigmoid(alpha g) * (u + 1)."""
 
     def __init__(self, hidden: int, n_experts: int, top: int, expert_ff: int, router_name: str, expert_names: Dict[str, str],
-                 shared: Optional[PartSpec] = None, shared_gate_name: Optional[str] = None):
+                 shared: Optional[PartSpec] = None, shared_gate_name: Optional[str] = None, router_bias_name: Optional[str] = None,
+                 weights: str = "sigmoid", weight_on: str = "input", act: str = "silu", limit: float = 0.0, alpha: float = 1.0):
         """expert_names: patterns of gate, up, down with {e} for the expert's index."""
+        if weights not in ops.ROUTE_WEIGHTS or weight_on not in ("input", "output") or act not in ops.MOE_ACTS:
+            raise ValueError(f"moe: unknown weighting '{weights}', weight placement '{weight_on}' or activation '{act}'")
+        if act == "swish_clamped" and not limit > 0:
+            raise ValueError(f"moe: the clamped activation needs a positive limit, got {limit!r}")
+        self.router_bias_name, self.weights, self.weight_on, self.act = router_bias_name, weights, weight_on, act
+        self.limit, self.alpha = float(limit), float(alpha)
         self.hidden, self.E, self.top, self.F = int(hidden), int(n_experts), int(top), int(expert_ff)
         if not (1 <= self.top <= self.E):
             raise ValueError(f"moe: {self.top} of {self.E} experts cannot be chosen")
@@ -100,6 +113,8 @@ class MoEFeedForward(Part):
 
     def weight_specs(self) -> List[WeightSpec]:
         specs = [WeightSpec(self.router_name, (self.E, self.hidden))]
+        if self.router_bias_name:
+            specs.append(WeightSpec(self.router_bias_name, (self.E,)))
         for e in range(self.E):
             n = {k: v.format(e=e) for k, v in self.expert_names.items()}
             specs += [WeightSpec(n["gate"], (self.F, self.hidden)), WeightSpec(n["up"], (self.F, self.hidden)),
@@ -117,6 +132,10 @@ class MoEFeedForward(Part):
         rows = [tensors[self.router_name]] + ([tensors[self.shared_gate_name]] if self.shared is not None else [])
         rdt = torch.bfloat16 if all(matrix_dtype(r.dtype, dtype) == torch.bfloat16 for r in rows) else torch.float32
         self.router = torch.cat([r.to(device=device, dtype=rdt) for r in rows], dim=0).contiguous()
+        self.router_bias = None
+        if self.router_bias_name:                # added to the 32-bit logits in the product's epilogue (nothing on the shared gate's)
+            self.router_bias = torch.zeros(self.router.shape[0], dtype=torch.float32, device=device)
+            self.router_bias[:self.E] = tensors[self.router_bias_name].to(device=device, dtype=torch.float32)
         names = [{k: v.format(e=e) for k, v in self.expert_names.items()} for e in range(self.E)]
         mdt = torch.bfloat16
         for n in names:
@@ -135,11 +154,13 @@ class MoEFeedForward(Part):
         T, dev = normed.shape[0], normed.device
         n_logits = self.router.shape[0]
         logits = scratch_buf("moe.logits", (T, n_logits), torch.float32, dev)
-        ops.linear(normed, self.router, logits)
-        routing = ops.moe_route(logits, self.E, self.top, ops.moe_tile_rows(normed, self.w_gate_up, self.dtype, self.top))
+        ops.linear(normed, self.router, logits, None, self.router_bias)
+        routing = ops.moe_route(logits, self.E, self.top, ops.moe_tile_rows(normed, self.w_gate_up, self.dtype, self.top),
+                                self.weights)
         act = scratch_buf("moe.act", (T * self.top, self.F), self.dtype, dev)
         parts = scratch_buf("moe.parts", (T, self.top, self.hidden), torch.float32, dev)
-        ops.moe_experts(normed, self.w_gate_up, self.w_down, routing, self.top, act, parts)
+        ops.moe_experts(normed, self.w_gate_up, self.w_down, routing, self.top, act, parts, self.act, self.weight_on, self.limit,
+                        self.alpha)
         if self.shared is None:
             return parts, None, None
         shared_out = scratch_buf("moe.shared", (T, self.hidden), torch.float32, dev)

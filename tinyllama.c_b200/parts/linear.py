@@ -29,21 +29,52 @@ def matrix_dtype(stored: torch.dtype, run: torch.dtype) -> torch.dtype:
 class StackedLinear:
     """Rows of several named weights (and optional biases) stacked into one projection."""
 
-    def __init__(self, in_features: int):
+    def __init__(self, in_features: int, in_heads: Optional[tuple] = None):
+        """in_heads = (n, have, want): the stored matrices have n * have columns, n heads of `have` values; the
+        projection reads n * want >= n * have values, every head followed by want - have that the weights ignore (zero
+        columns), as a producer that pads its heads leaves them."""
         self.in_features = int(in_features)
+        self.in_heads = tuple(int(v) for v in in_heads) if in_heads else None
+        if self.in_heads and (self.in_heads[0] * self.in_heads[2] != self.in_features or self.in_heads[1] > self.in_heads[2]):
+            raise ValueError(f"padded input heads {self.in_heads} do not make {self.in_features} input values")
         self.segments: List[dict] = []
         self.weight: Optional[torch.Tensor] = None
         self.colscale: Optional[torch.Tensor] = None
         self.colbias: Optional[torch.Tensor] = None
 
     def add(self, weight_name: str, rows: int, bias_name: Optional[str] = None, in_scale: float = 1.0,
-            out_scale=1.0) -> int:
+            out_scale=1.0, heads: Optional[tuple] = None) -> int:
         """Adds `rows` output rows; returns their first column in the stacked output.
-        y = ((x * in_scale) W^T + bias) * out_scale, out_scale a number or one value per row."""
+        y = ((x * in_scale) W^T + bias) * out_scale, out_scale a number or one value per row.
+        heads = (n, have, want): the stored matrix has n * have rows, n heads of `have`; the projection gives every head
+        `want` >= have outputs (rows = n * want), the extra ones zero."""
         off = self.out_features
+        if heads is not None:
+            heads = tuple(int(v) for v in heads)
+            if heads[0] * heads[2] != int(rows) or heads[1] > heads[2] or bias_name:
+                raise ValueError(f"padded heads {heads} do not make {rows} rows (and take no bias)")
         self.segments.append(dict(w=weight_name, b=bias_name, rows=int(rows), in_scale=float(in_scale),
-                                  out_scale=out_scale, off=off))
+                                  out_scale=out_scale, off=off, heads=heads))
         return off
+
+    def _stored_shape(self, seg: dict) -> tuple:
+        rows = seg["rows"] if not seg.get("heads") else seg["heads"][0] * seg["heads"][1]
+        cols = self.in_features if not self.in_heads else self.in_heads[0] * self.in_heads[1]
+        return (rows, cols)
+
+    def _laid_out(self, seg: dict, m: torch.Tensor) -> torch.Tensor:
+        """The stored matrix with zero rows / columns where heads are padded."""
+        if seg.get("heads"):
+            n, have, want = seg["heads"]
+            full = m.new_zeros((n, want, m.shape[1]))
+            full[:, :have] = m.reshape(n, have, m.shape[1])
+            m = full.reshape(n * want, m.shape[1])
+        if self.in_heads:
+            n, have, want = self.in_heads
+            full = m.new_zeros((m.shape[0], n, want))
+            full[:, :, :have] = m.reshape(m.shape[0], n, have)
+            m = full.reshape(m.shape[0], n * want)
+        return m
 
     @property
     def out_features(self) -> int:
@@ -52,13 +83,13 @@ class StackedLinear:
     def weight_specs(self) -> List[WeightSpec]:
         specs = []
         for s in self.segments:
-            specs.append(WeightSpec(s["w"], (s["rows"], self.in_features), "normal"))
+            specs.append(WeightSpec(s["w"], self._stored_shape(s), "normal"))
             if s["b"]:
                 specs.append(WeightSpec(s["b"], (s["rows"],), "normal"))
         return specs
 
     def bind(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:
-        mats = [tensors[s["w"]] for s in self.segments]
+        mats = [self._laid_out(s, tensors[s["w"]]) for s in self.segments]
         mdt = torch.bfloat16
         for m in mats:
             if matrix_dtype(m.dtype, dtype) == torch.float32:

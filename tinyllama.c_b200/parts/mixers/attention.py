@@ -5,6 +5,13 @@ rotation of q and k (falcon_h1.c:332-333), K/V write-through and causal attentio
 kv head h/(H/KV), scale 1/sqrt(head_dim) and an optional window (cpu_op.c:964-1064;
 graph.c:1275), output projection (falcon_h1.c:338).  The multipliers on the input, the
 keys and the output have no counterpart there; they fold into the projections.
+
+Options beyond that, each a constructor argument: tensor names of one's own; a score scale other than
+1/sqrt(head size); values of another size than the keys (the narrower of the two is padded with zero rows of
+its projection, so that the kernels see one head size); a rotation of neighbouring pairs (2i, 2i+1); queries and
+keys divided by their root mean square per head after the rotation (no weight); and an output gate, the
+concatenated heads times the sigmoid of one more projection of the mixer's input.  A rotation of neighbours and
+the norm run as one kernel on the 32-bit projection before keys and values are stored.
 """
 from __future__ import annotations
 
@@ -22,7 +29,14 @@ from ..linear import StackedLinear
 class AttentionMixer(Part):
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, prefix: str,
                  position: PartSpec, bias: bool = False, window: Optional[int] = None, in_scale: float = 1.0,
-                 out_scale: float = 1.0, key_scale: float = 1.0, cache_key: str = "kv"):
+                 out_scale: float = 1.0, key_scale: float = 1.0, cache_key: str = "kv",
+                 names: Optional[Dict[str, str]] = None, scale: Optional[float] = None, v_dim: Optional[int] = None,
+                 qk_norm_eps: Optional[float] = None, gate: Optional[str] = None):
+        """names: tensor names of q, k, v, o (and g, the gate's projection) after the prefix, where they are not the
+        q_proj.weight ... of the architecture's checkpoints (biases then take no part).  scale: what scores are
+        multiplied by (default head_dim ** -0.5).  v_dim: size of a value head (default head_dim).  qk_norm_eps: queries
+        and keys are divided by sqrt(mean(x^2) + eps) per head after the rotation.  gate: "sigmoid" or "silu" of the
+        projection named g multiplies the heads' results."""
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} key/value heads")
         if not (1 <= int(head_dim) <= ops.MAX_HEAD_DIM):
@@ -30,20 +44,42 @@ class AttentionMixer(Part):
                              f"(1..{ops.MAX_HEAD_DIM})")
         if int(n_heads) > ops.MAX_HEADS:
             raise ValueError(f"attention: {n_heads} heads exceed the kernels' limit of {ops.MAX_HEADS}")
-        self.hidden, self.H, self.KV, self.hd = int(hidden), int(n_heads), int(n_kv_heads), int(head_dim)
+        self.qk_dim, self.v_dim = int(head_dim), int(v_dim) if v_dim else int(head_dim)
+        if not (1 <= self.v_dim <= ops.MAX_HEAD_DIM):
+            raise ValueError(f"attention: value size {self.v_dim} is outside what the kernels are built for (1..{ops.MAX_HEAD_DIM})")
+        # one head size for the kernels: the wider of keys and values; the other is padded with zeros
+        self.hidden, self.H, self.KV, self.hd = int(hidden), int(n_heads), int(n_kv_heads), max(self.qk_dim, self.v_dim)
         self.window = int(window) if window else None
         self.cache_key = cache_key
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.qk_dim)
+        self.qk_norm_eps = float(qk_norm_eps) if qk_norm_eps is not None else None
+        if gate is not None and gate not in ops.GATES:
+            raise ValueError(f"attention: unknown output gate '{gate}'; known: {sorted(ops.GATES)}")
+        self.gate = gate
         self.position = position.build()
-        if getattr(self.position, "layout", "split_half") != "split_half":
-            raise ValueError(f"attention: the kernels of this mixer rotate split-half pairs; position part "
-                             f"'{position.name}' pairs dimensions as '{self.position.layout}'")
+        layout = getattr(self.position, "layout", "split_half")
+        if layout not in ("split_half", "interleaved"):
+            raise ValueError(f"attention: the kernels of this mixer rotate split-half or neighbouring pairs; position part "
+                             f"'{position.name}' pairs dimensions as '{layout}'")
+        # neighbouring pairs and the norm after the rotation are one kernel on the projection; the kernels that store
+        # keys and values (which rotate split-half pairs themselves) then rotate nothing
+        self.pre_transform = layout == "interleaved" or self.qk_norm_eps is not None
+        if names is not None and bias:
+            raise ValueError("attention: tensor names of one's own take no biases")
+        nm = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight")
+        nm.update(names or {})
+        if self.gate and "g" not in nm:
+            raise ValueError("attention: an output gate needs the name of its projection ('g')")
         b = (lambda n: prefix + n + ".bias") if bias else (lambda n: None)
+        qk_heads = lambda n: (n, self.qk_dim, self.hd) if self.qk_dim != self.hd else None
+        v_heads = lambda n: (n, self.v_dim, self.hd) if self.v_dim != self.hd else None
         self.qkv = StackedLinear(hidden)
-        self.q_off = self.qkv.add(prefix + "q_proj.weight", self.H * self.hd, b("q_proj"), in_scale)
-        self.k_off = self.qkv.add(prefix + "k_proj.weight", self.KV * self.hd, b("k_proj"), in_scale, key_scale)
-        self.v_off = self.qkv.add(prefix + "v_proj.weight", self.KV * self.hd, b("v_proj"), in_scale)
-        self.o = StackedLinear(self.H * self.hd)
-        self.o.add(prefix + "o_proj.weight", hidden, b("o_proj"), 1.0, out_scale)
+        self.q_off = self.qkv.add(prefix + nm["q"], self.H * self.hd, b("q_proj"), in_scale, heads=qk_heads(self.H))
+        self.k_off = self.qkv.add(prefix + nm["k"], self.KV * self.hd, b("k_proj"), in_scale, key_scale, heads=qk_heads(self.KV))
+        self.v_off = self.qkv.add(prefix + nm["v"], self.KV * self.hd, b("v_proj"), in_scale, heads=v_heads(self.KV))
+        self.g_off = self.qkv.add(prefix + nm["g"], self.H * self.hd, None, in_scale, heads=v_heads(self.H)) if self.gate else None
+        self.o = StackedLinear(self.H * self.hd, in_heads=v_heads(self.H))
+        self.o.add(prefix + nm["o"], hidden, b("o_proj"), 1.0, out_scale)
         self.dtype = None
 
     @property
@@ -54,7 +90,7 @@ class AttentionMixer(Part):
         fused = self.dtype == torch.bfloat16 and self.position.rotation_table() is not None \
             and ops.library().tlc_attention_decode_fused_ok(self.H, self.KV, self.hd) \
             and not ops.DISABLE_FUSED_DECODE_ATTENTION
-        return 1 if fused else 3
+        return (1 if fused else 3) + int(self.pre_transform) + int(self.gate is not None)
 
     def weight_specs(self) -> List[WeightSpec]:
         return self.qkv.weight_specs() + self.o.weight_specs() + self.position.weight_specs()
@@ -105,22 +141,31 @@ class AttentionMixer(Part):
             # not a rotation: the part changes q and k in place; what is stored below is its result
             self.position.transform(qkv, self.q_off, self.k_off, step, self.H, self.KV, self.hd)
             table = self._no_rotation
+        if self.pre_transform:
+            ops.qk_rotate_norm(qkv, self.q_off, self.k_off, self.H, self.KV, self.hd, self.qk_dim, table,
+                               getattr(self.position, "layout", "split_half") == "interleaved", self.qk_norm_eps, step.positions)
+            table = self._no_rotation
         if step.max_new == 1 and ops.attention_decode_fused_ok(qkv, self.dtype, self.H, self.KV, self.hd):
             # one token per sequence: rotation, store and attention in one kernel
             att = out if out is not None else scratch_buf(f"attention.{self.cache_key}.out", (T, self.H * self.hd), self.dtype, qkv.device)
             ops.attention_decode_fused(qkv, self.q_off, self.k_off, self.v_off, kv.k_pages, kv.v_pages, table,
                                        cache.writes, kv.block_table, step.positions, step.row_seq, step.slots, att,
-                                       self.H, self.KV, self.hd, 1.0 / math.sqrt(self.hd), self.window or 0,
+                                       self.H, self.KV, self.hd, self.scale, self.window or 0,
                                        step.max_context, self._arrivals)
-            return att
+            return self._gated(att, qkv)
         q = scratch_buf(f"attention.{self.cache_key}.q", (T, self.H * self.hd), self.dtype, qkv.device)
         ops.rope_kv_store(qkv, self.q_off, self.k_off, self.v_off, q, kv.k_pages, kv.v_pages, table, step.positions,
                           step.row_seq, step.slots, kv.block_table, self.H, self.KV, self.hd, cache.writes)
         att = out if out is not None else scratch_buf(f"attention.{self.cache_key}.out", (T, self.H * self.hd), self.dtype, qkv.device)
         ops.attention(q, kv.k_pages, kv.v_pages, kv.block_table, step.positions, step.row_seq, step.slots, att,
-                      self.H, self.KV, self.hd, 1.0 / math.sqrt(self.hd), self.window or 0,
+                      self.H, self.KV, self.hd, self.scale, self.window or 0,
                       step.max_context if step.max_new == 1 else 0, step.cu_seqlens, step.start_pos, step.max_context,
                       max_blocks)
+        return self._gated(att, qkv)
+
+    def _gated(self, att: torch.Tensor, qkv: torch.Tensor) -> torch.Tensor:
+        if self.gate:
+            ops.gate_mul(att, qkv[:, self.g_off:self.g_off + self.H * self.hd], self.gate)
         return att
 
     def output(self, att: torch.Tensor, residual: torch.Tensor) -> None:

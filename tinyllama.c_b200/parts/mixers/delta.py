@@ -1,0 +1,106 @@
+"""Gated delta-rule mixer: a recurrence whose state is a matrix per head that every token corrects towards its own
+(key, value) pair.
+
+From the mixer's input h: q = W_q h and k = W_k h (G heads of dk values), v = W_v h (H heads of dv values; head i uses
+q/k head i // (H / G)).  Each of q, k, v passes a short causal convolution over time per channel (weights [channels,
+taps], the last tap on the current token, zeros before the sequence's start) and SiLU; q and k then become unit vectors
+per head, x / sqrt(sum(x^2) + l2_eps), the query also times q_scale (dk ** -0.5 unless given).  Per head
+beta = sigmoid(W_b h) and the decay g = exp(-exp(A_log) * softplus(W_a h + dt_bias)), and
+
+    S <- g S;    u = beta (v - S^T k);    S <- S + k u^T;    o = S^T q
+
+in this order.  Every head's o is divided by its root mean square over dv, multiplied by a weight [dv] that the heads
+share and by silu(W_g h), and W_o maps the heads' results back.  S [H, dk, dv] and the last taps - 1 inputs of the
+convolution are kept per sequence between steps (32-bit; a sequence at position 0 starts from zeros); everything
+between the projections and the output projection is 32-bit.
+
+The six projections of h are one product.  The convolution (with the decay beside it: dt = softplus(a + dt_bias),
+decay = exp(dt * -exp(A_log))) is the kernel that serves every short convolution of the library.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ... import ops
+from ..base import LayerCache, Part, StateRequest, StepInfo, WeightSpec, register_mixer, scratch_buf, to_vec
+from ..linear import StackedLinear
+
+
+@register_mixer("delta")
+class DeltaMixer(Part):
+    def __init__(self, hidden: int, n_heads: int, n_qk_heads: int, key_dim: int, v_dim: int, conv_taps: int, eps: float,
+                 names: Dict[str, str], l2_eps: float = 1e-6, q_scale: Optional[float] = None, cache_key: str = "delta"):
+        """names: tensor names of q, k, v (their convolutions are these names + '.conv'), b, a, A_log, dt_bias, norm, g, o.
+        eps: of the output norm."""
+        self.hidden, self.H, self.G, self.dk, self.dv, self.K = (int(hidden), int(n_heads), int(n_qk_heads), int(key_dim),
+                                                                 int(v_dim), int(conv_taps))
+        if self.H % self.G:
+            raise ValueError(f"delta: {self.H} heads are not a multiple of {self.G} query/key heads")
+        if not (1 <= self.dk <= ops.MAX_DELTA_KEY_DIM):
+            raise ValueError(f"delta: keys of {self.dk} values are outside what the kernel is built for (1..{ops.MAX_DELTA_KEY_DIM})")
+        if not (1 <= self.K <= ops.MAX_CONV_TAPS):
+            raise ValueError(f"delta: {self.K} convolution taps are outside what the kernels are built for (1..{ops.MAX_CONV_TAPS})")
+        if self.H > ops.MAX_HEADS:
+            raise ValueError(f"delta: {self.H} heads exceed the kernels' limit of {ops.MAX_HEADS}")
+        self.eps, self.l2_eps = float(eps), float(l2_eps)
+        self.q_scale = float(q_scale) if q_scale is not None else self.dk ** -0.5
+        self.names, self.cache_key = dict(names), cache_key
+        n = self.names
+        self.Cd = 2 * self.G * self.dk + self.H * self.dv          # channels of the convolution: q | k | v
+        self.proj = StackedLinear(hidden)
+        self.q_off = self.proj.add(n["q"], self.G * self.dk)
+        self.k_off = self.proj.add(n["k"], self.G * self.dk)
+        self.v_off = self.proj.add(n["v"], self.H * self.dv)
+        self.a_off = self.proj.add(n["a"], self.H)
+        self.b_off = self.proj.add(n["b"], self.H)
+        self.g_off = self.proj.add(n["g"], self.H * self.dv)
+        self.o = StackedLinear(self.H * self.dv)
+        self.o.add(n["o"], hidden)
+        self.dtype = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        n = self.names
+        return self.proj.weight_specs() + self.o.weight_specs() + [
+            WeightSpec(n["q"] + ".conv", (self.G * self.dk, self.K), "conv"), WeightSpec(n["k"] + ".conv", (self.G * self.dk, self.K), "conv"),
+            WeightSpec(n["v"] + ".conv", (self.H * self.dv, self.K), "conv"), WeightSpec(n["A_log"], (self.H,), "a_log"),
+            WeightSpec(n["dt_bias"], (self.H,), "dt_bias"), WeightSpec(n["norm"], (self.dv,), "ones")]
+
+    def cache_requests(self) -> list:
+        return [StateRequest(self.cache_key + ".conv", (self.K - 1, self.Cd)),
+                StateRequest(self.cache_key + ".state", (self.H, self.dk, self.dv))]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
+        n = self.names
+        self.dtype = dtype
+        self.proj.bind(tensors, dtype, device)
+        self.o.bind(tensors, dtype, device)
+        self.conv_w = to_vec(torch.cat([tensors[n[x] + ".conv"].to(torch.float32).reshape(-1, self.K) for x in ("q", "k", "v")], dim=0),
+                             device)
+        self.A = (-torch.exp(tensors[n["A_log"]].to(torch.float32))).to(device).contiguous()      # decay = exp(dt * A)
+        self.dt_bias = to_vec(tensors[n["dt_bias"]], device)
+        self.norm_w = to_vec(tensors[n["norm"]], device).repeat(self.H).contiguous()              # one weight for every head
+
+    def forward(self, normed: torch.Tensor, step: StepInfo, cache: LayerCache, residual: torch.Tensor,
+                accumulate: bool = True) -> None:
+        if not (cache.writes and cache.kv_writes):
+            raise ValueError("delta: a recurrent mixer cannot run on another layer's cache without storing "
+                             "(its window and state would advance twice in one step)")
+        T, dev, f32 = step.n_rows, normed.device, torch.float32
+        new = lambda tag, shape, dt: scratch_buf(f"delta.{self.cache_key}.{tag}", shape, dt, dev)
+        proj = new("proj", (T, self.proj.out_features), f32)
+        self.proj.forward(normed, proj)
+        qkv = new("qkv", (T, self.Cd), f32)
+        dt, decay = new("dt", (T, self.H), f32), new("decay", (T, self.H), f32)
+        ops.mamba_conv(proj, self.q_off, self.a_off, self.conv_w, None, self.dt_bias, self.A, cache.state[self.cache_key + ".conv"],
+                       step.cu_seqlens, step.row_seq, step.slots, step.start_pos, qkv, dt, decay, step.max_new == 1, False,
+                       len(step.host_start) == step.n_seqs and not any(step.host_start))
+        beta = new("beta", (T, self.H), f32)
+        ops.delta_prepare(qkv, self.q_off, self.k_off, self.G, self.dk, self.l2_eps, self.q_scale, proj, self.b_off, self.H, beta)
+        y = new("y", (T, self.H * self.dv), f32)
+        ops.delta_rule(qkv, self.q_off, self.k_off, self.v_off, beta, decay, cache.state[self.cache_key + ".state"], step, y,
+                       self.H, self.G, self.dk, self.dv)
+        gated = new("gated", (T, self.H * self.dv), self.dtype)
+        ops.gated_rmsnorm(y, proj[:, self.g_off:self.g_off + self.H * self.dv], self.norm_w, self.eps, self.H, True, gated)
+        self.o.forward(gated, residual, accumulate=accumulate)

@@ -12,6 +12,10 @@ The keys are never built: qn_i . U_i c = (U_i^T qn_i) . c, so the query is carri
 and collects sum_j p_j c_j, and V_i is applied to that sum afterwards.  A layer may attend over the rows
 that ANOTHER layer cached (LayerRun.kv_cache) with its own queries, U, V and sink; it then has no
 down-projection.
+
+Options: no rotated part at all (rot_dim 0 with the position part "none": attention without positions); no sink
+(names without 'sink'); queries through a latent of their own (q_rank: c_q = RMSnorm(W_dq h) * w, q = W_uq c_q, names
+dq, dq_norm, uq instead of q); a sliding window (a row sees itself and the window - 1 rows before it).
 """
 from __future__ import annotations
 
@@ -27,9 +31,12 @@ from ..linear import StackedLinear, matrix_dtype
 @register_mixer("latent_attention")
 class LatentAttentionMixer(Part):
     def __init__(self, hidden: int, n_heads: int, head_dim: int, rot_dim: int, v_dim: int, kv_rank: int, scale: float,
-                 eps: float, position: PartSpec, names: Dict[str, str], own_latent: bool = True, cache_key: str = "latent"):
-        """names: tensor names of q, dkv, dkv_norm, uk, uv, sink, o.  own_latent False: the layer has no down-projection
-        and reads the rows of the entry that its run-order entry names."""
+                 eps: float, position: PartSpec, names: Dict[str, str], own_latent: bool = True, cache_key: str = "latent",
+                 q_rank: Optional[int] = None, window: Optional[int] = None, cache_window: Optional[int] = None):
+        """names: tensor names of q (or, with q_rank, of dq, dq_norm, uq), dkv, dkv_norm, uk, uv, o and optionally sink.
+        own_latent False: the layer has no down-projection and reads the rows of the entry that its run-order entry names.
+        window: how many keys a row sees, itself included (None: all).  cache_window: how many rows back the cache must
+        keep (None: all); a layer whose rows other layers read with windows of their own is given the widest."""
         self.hidden, self.H, self.dn, self.r, self.dv, self.R = (int(hidden), int(n_heads), int(head_dim), int(rot_dim),
                                                                  int(v_dim), int(kv_rank))
         if not (1 <= self.R <= ops.MAX_LATENT):
@@ -42,8 +49,21 @@ class LatentAttentionMixer(Part):
         if getattr(self.position, "layout", None) != "interleaved" and position.name != "none":
             raise ValueError(f"latent_attention: the kernels of this mixer rotate interleaved pairs; position part "
                              f"'{position.name}' does not")
+        self.window = int(window) if window else None
+        self.cache_window = int(cache_window) if cache_window else None
+        if self.window and self.cache_window and self.cache_window < self.window:
+            raise ValueError(f"latent_attention: a cache that keeps {self.cache_window} rows cannot serve a window of {self.window}")
+        self.q_rank = int(q_rank) if q_rank else None
         self.proj = StackedLinear(hidden)
-        self.q_off = self.proj.add(names["q"], self.H * (self.dn + self.r))
+        if self.q_rank:
+            # queries through a latent: the first product gives c_q's pre-norm values (and the down-projection), a second
+            # one the queries
+            self.q_off = self.proj.add(names["dq"], self.q_rank)
+            self.uq = StackedLinear(self.q_rank)
+            self.uq.add(names["uq"], self.H * (self.dn + self.r))
+        else:
+            self.q_off = self.proj.add(names["q"], self.H * (self.dn + self.r))
+            self.uq = None
         self.dkv_off = self.proj.add(names["dkv"], self.R + self.r) if self.own_latent else None
         self.o = StackedLinear(self.H * self.dv)
         self.o.add(names["o"], hidden)
@@ -52,14 +72,17 @@ class LatentAttentionMixer(Part):
     def weight_specs(self) -> List[WeightSpec]:
         n = self.names
         specs = self.proj.weight_specs() + self.o.weight_specs()
-        specs += [WeightSpec(n["uk"], (self.H * self.dn, self.R)), WeightSpec(n["uv"], (self.H * self.dv, self.R)),
-                  WeightSpec(n["sink"], (self.H,))]
+        specs += [WeightSpec(n["uk"], (self.H * self.dn, self.R)), WeightSpec(n["uv"], (self.H * self.dv, self.R))]
+        if n.get("sink"):
+            specs.append(WeightSpec(n["sink"], (self.H,)))
+        if self.q_rank:
+            specs += self.uq.weight_specs() + [WeightSpec(n["dq_norm"], (self.q_rank,), "ones")]
         if self.own_latent:
             specs.append(WeightSpec(n["dkv_norm"], (self.R,), "ones"))
         return specs
 
     def cache_requests(self) -> list:
-        return [KVRequest(self.cache_key, 1, self.R + self.r, None, values=False)]
+        return [KVRequest(self.cache_key, 1, self.R + self.r, self.cache_window, values=False)]
 
     def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
         n = self.names
@@ -72,7 +95,10 @@ class LatentAttentionMixer(Part):
         # U_i^T as the weight [R, dn] of head i's product into the latent space; V_i [dv, R] as it is stored
         self.uk_t = uk.to(device=device, dtype=mdt).reshape(self.H, self.dn, self.R).transpose(1, 2).contiguous()
         self.uv = uv.to(device=device, dtype=matrix_dtype(uv.dtype, dtype)).reshape(self.H, self.dv, self.R).contiguous()
-        self.sink = to_vec(tensors[n["sink"]], device)
+        self.sink = to_vec(tensors[n["sink"]], device) if n.get("sink") else None
+        if self.q_rank:
+            self.uq.bind(tensors, dtype, device)
+            self.q_norm = to_vec(tensors[n["dq_norm"]], device)
         self.c_norm = to_vec(tensors[n["dkv_norm"]], device) if self.own_latent else None
 
     def forward(self, normed: torch.Tensor, step: StepInfo, cache: LayerCache, residual: torch.Tensor,
@@ -89,11 +115,17 @@ class LatentAttentionMixer(Part):
         qn = new("qn", (T, H * dn), self.dtype)
         qa = new("qa", (T, H * (R + r)), self.dtype)
         pages = kv.k_pages.view(kv.k_pages.shape[0], ops.PAGE, R + r)        # one key/value head
-        ops.latent_prepare(proj, self.q_off, self.dkv_off, self.c_norm, self.eps, self.position.rotation_table(), step,
-                           kv.block_table, pages, qn, qa, H, dn, r, R)
+        q_proj, q_off = None, self.q_off
+        if self.q_rank:
+            cq = new("cq", (T, self.q_rank), self.dtype)
+            ops.rmsnorm(proj[:, self.q_off:self.q_off + self.q_rank], self.q_norm, self.eps, cq)
+            q_proj, q_off = new("q", (T, self.uq.out_features), torch.float32), 0
+            self.uq.forward(cq, q_proj)
+        ops.latent_prepare(proj, q_off, self.dkv_off, self.c_norm, self.eps, self.position.rotation_table(), step,
+                           kv.block_table, pages, qn, qa, H, dn, r, R, q_proj)
         ops.linear_heads(qn, dn, self.uk_t, qa, R + r)                       # qa[:, i, :R] = U_i^T qn_i
         lat = new("lat", (T, H * R), self.dtype)
-        ops.latent_attention(qa, pages, self.sink, kv.block_table, step, lat, H, R, r, self.scale)
+        ops.latent_attention(qa, pages, self.sink, kv.block_table, step, lat, H, R, r, self.scale, window=self.window or 0)
         att = new("att", (T, H * dv), self.dtype)
         ops.linear_heads(lat, R, self.uv, att, dv)                           # att[:, i] = V_i (sum_j p_j c_j)
         self.o.forward(att, residual, accumulate=accumulate)
