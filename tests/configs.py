@@ -75,3 +75,52 @@ TUREVIK_B = dict(architecture="Turevik", vocab=97, width=44, norm=dict(eps=1e-6)
 ])
 
 TUREVIK = {"TA": TUREVIK_A, "TB": TUREVIK_B}
+
+
+# ---- Porarax ---------------------------------------------------------------------------------------------------
+def _p_latent(heads, dim, vdim, kv_rank, q_rank, scale, window, kv_from=None):
+    m = dict(heads=heads, dim=dim, vdim=vdim, kv_rank=kv_rank, q_rank=q_rank, scale=scale, mask=dict(size=window))
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return dict(type="latent_attention", mixer=m)
+
+
+def _p_attention(heads, kv_heads, dim, vdim, scale, base, dims):
+    return dict(type="attention", mixer=dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=scale,
+                                             rot=dict(base=base, dims=dims)))
+
+
+def _p_delta(heads, kv_heads, dim, vdim, conv):
+    return dict(type="delta", mixer=dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, conv=conv))
+
+
+def _p_moe(experts, top, ff, limit):
+    return dict(kind="moe", router=dict(experts=experts, top=top), expert=dict(ff=ff, limit=limit))
+
+
+# A: a recurrent layer first; values wider than keys in an attention layer (padded heads) and three rotated pairs of
+# many; a layer that reads another layer's latents with a WIDER window than the owner's and other head sizes; a layer
+# without feed-forward; all experts chosen; a single expert
+PORARAX_A = dict(architecture="Porarax", vocab=150, width=64, norm=dict(eps=1e-5), layers=[
+    dict(_p_delta(4, 2, 16, 24, 3), mlp=_p_moe(5, 2, 24, 1.5)),
+    dict(_p_latent(3, 16, 8, 32, 24, 0.3, 70), mlp=_p_moe(4, 4, 16, 3.0)),
+    dict(_p_attention(4, 2, 32, 32, 0.2, 1000.0, 16), mlp=None),
+    dict(_p_latent(2, 8, 16, 32, 16, 0.4, 100, kv_from=1), mlp=_p_moe(1, 1, 40, 2.5)),
+    dict(_p_attention(6, 1, 16, 40, 0.5, 50.0, 6), mlp=_p_moe(6, 3, 8, 0.75)),
+])
+
+# B: widths that are no multiples of 8; one head; a window of five keys and one of exactly a page; a latent that is no
+# multiple of 16 (the warp kernel also in bfloat16); heads of 64 (the tensor-core attention of prompts, the one-kernel
+# attention of single tokens) fully rotated; keys wider than values; two and five convolution taps, one query/key head
+# for three value heads; an attention layer that rotates nothing; a reader with a NARROWER window than the owner's
+PORARAX_B = dict(architecture="Porarax", vocab=97, width=44, norm=dict(eps=1e-6), layers=[
+    dict(_p_latent(1, 12, 20, 48, 10, 0.5, 5), mlp=_p_moe(3, 3, 20, 1.0)),
+    dict(_p_attention(2, 2, 64, 64, 0.11, 10000.0, 64), mlp=_p_moe(7, 2, 12, 0.5)),
+    dict(_p_delta(2, 2, 40, 12, 2), mlp=None),
+    dict(_p_latent(5, 8, 8, 20, 32, 0.35, 64), mlp=_p_moe(2, 1, 16, 4.0)),
+    dict(_p_delta(3, 1, 8, 8, 5), mlp=_p_moe(4, 2, 28, 2.0)),
+    dict(_p_latent(2, 24, 4, 20, 8, 0.2, 33, kv_from=3), mlp=_p_moe(5, 5, 12, 1.25)),
+    dict(_p_attention(3, 3, 20, 12, 0.3, 100.0, 0), mlp=_p_moe(2, 2, 36, 6.0)),
+])
+
+PORARAX = {"PA": PORARAX_A, "PB": PORARAX_B}
