@@ -245,9 +245,10 @@ def main() -> int:
     ap.add_argument("--no-big", dest="big", action="store_false", help="skip the 3B and 7B workloads among the points")
     ap.add_argument("--no-pairs", action="store_true", help="run the linear layers on single blocks (128 x 256 tiles) instead "
                     "of pairs of blocks on 256 x 256 tiles: the comparison behind profiles/linear_tcgen05_prefill_2048.md")
-    ap.add_argument("--design", default=None, choices=["turevik"], help="instead of the benchmark line: prefill and decode "
-                    "throughput of this design at layer sizes of a real model's order (random weights), beside Falcon-H1 at "
-                    "equal width and layer count")
+    ap.add_argument("--design", default=None, choices=["turevik", "porarax"], help="instead of the benchmark line: prefill and decode "
+                    "throughput of this design at layer sizes of a real model's order (random weights), beside the library's "
+                    "closest other design (Falcon-H1 for turevik, Turevik for porarax) at equal width and layer count")
+    ap.add_argument("--sizes-only", default=None, choices=["width 2048", "width 3072"], help="with --design: one of the two sizes")
     ap.add_argument("--ref-budget", type=float, default=600.0, help="seconds the reference arm may take (it runs fewer "
                     "layers, and says so, where all of them would take longer)")
     args = ap.parse_args()
@@ -379,34 +380,91 @@ def turevik_work(cfg, batch, context, T):
     return fixed * 2 + expert_bytes + cache_bytes, 2.0 * (act_params - V * D) * T + 2.0 * V * D + att_flops   # the head on one row
 
 
+def porarax_config(width, heads, kv_heads, kv_rank, q_rank, window, experts, top, expert_ff, vocab):
+    """Four layers with every kind of mixer, experts beside each: latent attention over a window with latents of its own;
+    grouped-query attention (half of every head rotated); latent attention over the first layer's latents; the gated
+    delta rule."""
+    att = lambda **kw: dict(type="latent_attention", mixer=dict(heads=heads, dim=128, vdim=128, kv_rank=kv_rank, q_rank=q_rank,
+                                                                scale=128 ** -0.5, mask=dict(size=window), **kw))
+    moe = dict(kind="moe", router=dict(experts=experts, top=top), expert=dict(ff=expert_ff, limit=7.0))
+    return dict(architecture="Porarax", vocab=vocab, width=width, norm=dict(eps=1e-6), layers=[
+        dict(att(), mlp=moe),
+        dict(type="attention", mixer=dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5,
+                                          rot=dict(base=500000.0, dims=64)), mlp=moe),
+        dict(att(kv_from=0), mlp=moe),
+        dict(type="delta", mixer=dict(heads=heads, kv_heads=heads // 2, dim=128, vdim=128, conv=4), mlp=moe)])
+
+
+def porarax_work(cfg, batch, context, T):
+    """(bytes a decode step of `batch` sequences at `context` must read, FLOPs of a prompt of T tokens)."""
+    D, V = cfg["width"], cfg["vocab"]
+    fixed, cache_bytes, mix_flops, expert_bytes, expert_params = V * D, 0, 0.0, 0.0, 0
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        H, dk, dv = m["heads"], m["dim"], m["vdim"]
+        if layer["type"] == "latent_attention":
+            R, qr, W = m["kv_rank"], m["q_rank"], m["mask"]["size"]
+            fixed += qr * D + H * dk * qr + H * dk * R + H * dv * R + D * H * dv + (0 if "kv_from" in m else R * D)
+            cache_bytes += batch * min(context, W) * R * 2
+            keys = sum(min(t + 1, W) for t in range(T)) if T > 1 else 1
+            mix_flops += 2.0 * H * 2 * R * keys                       # scores and sums in the latent space
+        elif layer["type"] == "attention":
+            G = m["kv_heads"]
+            fixed += (H * dk + G * dk + G * dv + H * dv) * D + D * H * dv
+            cache_bytes += batch * context * G * (dk + dv) * 2
+            mix_flops += 2.0 * H * (dk + dv) * T * (T + 1) / 2
+        else:
+            G = m["kv_heads"]
+            fixed += (2 * G * dk + 2 * H * dv + 2 * H) * D + D * H * dv
+            cache_bytes += batch * H * dk * dv * 4                    # the state, 32-bit
+            mix_flops += 6.0 * H * dk * dv * T                        # S^T k, k u^T, S^T q
+        mlp = layer["mlp"]
+        E, top, F = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"]
+        fixed += E * D
+        expert_params += top * 3 * D * F
+        touched = E * (1.0 - (1.0 - 1.0 / E) ** (batch * top))              # expected distinct experts of a step
+        expert_bytes += touched * 3 * D * F * 2
+    return fixed * 2 + expert_bytes + cache_bytes, 2.0 * (fixed - V * D + expert_params) * T + 2.0 * V * D + mix_flops
+
+
 def design_compare(args) -> int:
-    """Turevik beside Falcon-H1 at equal width and layer count: a prompt of --prefill-tokens tokens and decode steps at
-    batch 8 and 64 from --prompt-len-token prompts, each as time and as a fraction of the measured peak for the bytes a
-    step must read (decode) or the FLOPs a prompt needs (prefill)."""
+    """Another design beside the library's closest one at equal width and layer count (Turevik beside Falcon-H1, Porarax
+    beside Turevik): a prompt of --prefill-tokens tokens and decode steps at batch 8 and 64 from --prompt-len-token
+    prompts, each as time and as a fraction of the measured peak for the bytes a step must read (decode) or the FLOPs a
+    prompt needs (prefill)."""
     import torch
     import tinyllama_c_b200 as tlc
     pk = peaks()
     T, out = args.prefill_tokens, {}
-    cases = {
-        "width 2048": (turevik_config(2048, 16, 256, 4096, 32, 4, 1024, 1024, 4096, 65536), dict(CONFIG_1P5B, num_hidden_layers=4)),
-        "width 3072": (turevik_config(3072, 24, 256, 12288, 64, 6, 2048, 2048, 6144, 130048), dict(CONFIG_7B, num_hidden_layers=4)),
-    }
+    turevik = {"width 2048": turevik_config(2048, 16, 256, 4096, 32, 4, 1024, 1024, 4096, 65536),
+               "width 3072": turevik_config(3072, 24, 256, 12288, 64, 6, 2048, 2048, 6144, 130048)}
+    if args.design == "porarax":
+        cases = {"width 2048": (porarax_config(2048, 16, 4, 256, 768, 1024, 32, 4, 1024, 65536), turevik["width 2048"]),
+                 "width 3072": (porarax_config(3072, 24, 8, 256, 1024, 1024, 64, 6, 2048, 130048), turevik["width 3072"])}
+        beside = "turevik"
+    else:
+        cases = {"width 2048": (turevik["width 2048"], dict(CONFIG_1P5B, num_hidden_layers=4)),
+                 "width 3072": (turevik["width 3072"], dict(CONFIG_7B, num_hidden_layers=4))}
+        beside = "falcon_h1"
+    work = {"turevik": turevik_work, "porarax": porarax_work}
+    if args.sizes_only:
+        cases = {k: v for k, v in cases.items() if k == args.sizes_only}
     for name, (tcfg, fcfg) in cases.items():
-        for design, cfg in (("turevik", tcfg), ("falcon_h1", fcfg)):
+        for design, cfg in ((args.design, tcfg), (beside, fcfg)):
             model = tlc.random_model(cfg, seed=0, dtype="bfloat16")
             llm = tlc.LLM(model, max_tokens=64 * (args.prompt_len + 2 * args.steps + 128) + T, max_seqs=64)
             row = {}
             pms = time_prefill(llm, T, seed=3)
             ctx = args.prompt_len + args.steps // 2
-            if design == "turevik":
-                flops = turevik_work(cfg, 1, 0, T)[1]
+            if design in work:
+                flops = work[design](cfg, 1, 0, T)[1]
             else:
                 flops = prefill_flops(cfg, T)
             row["prefill"] = {"tokens": T, "ms": round(pms, 3), "tok_s": round(T * 1000.0 / pms, 1),
                               "frac_of_measured_bf16": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
             for batch in (8, 64):
                 ms, launches, clocks, ctx = time_decode(llm, tlc, batch, args.prompt_len, args.steps, args.warmup, seed=1)
-                nbytes = turevik_work(cfg, batch, ctx, 1)[0] if design == "turevik" else decode_bytes(cfg, batch, ctx)
+                nbytes = work[design](cfg, batch, ctx, 1)[0] if design in work else decode_bytes(cfg, batch, ctx)
                 row[f"decode_batch_{batch}"] = {"ms_per_step": round(ms, 4), "tok_s": round(batch * 1000.0 / ms, 1),
                                                 "launches_per_step": launches // args.steps,
                                                 "frac_of_measured_hbm": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4),

@@ -48,17 +48,29 @@ extern "C" int tlc_delta_prepare(float* qkv, int ld, int q_off, int k_off, int G
 
 #define DELTA_COLS 32     // columns of S a block takes
 
-// Thread (c, s), s the fastest index: column j0 + c, rows s, s + NS, s + 2 NS, ... of S.
-template <int DKQ, int NS>
+__device__ __forceinline__ void delta_cp4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void delta_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void delta_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Thread (c, s), s the fastest index: column j0 + c, rows s, s + NS, s + 2 NS, ... of S.  The tokens' keys, queries,
+// values, decays and write strengths arrive in tiles of TT tokens by cp.async, the next tile while the current one
+// is walked: a token's step is then arithmetic and two rounds of shuffles, with no trip to memory on its path.
+// TT: tokens of a tile that is staged in shared memory (two tiles: one in use, one on its way).
+template <int DKQ, int NS, int TT>
 __global__ void __launch_bounds__(DELTA_COLS * NS)
 delta_rule_kernel(const float* __restrict__ qkv, int ld, int q_off, int k_off, int v_off, const float* __restrict__ beta,
                   const float* __restrict__ decay, float* state, const int* __restrict__ cu_seqlens,
                   const int* __restrict__ slots, const int* __restrict__ start_pos, int H, int G, int dk, int dv,
                   float* __restrict__ y, int ldy) {
   tlc_pdl(qkv, beta, decay, state, y);
-  const int b = blockIdx.z, h = blockIdx.y;
-  const int c = threadIdx.x / NS, s = threadIdx.x % NS;
-  const int j = blockIdx.x * DELTA_COLS + c;
+  constexpr int NT = DELTA_COLS * NS, DKP = DKQ * NS;
+  constexpr int STAGE = TT * (2 * DKP + DELTA_COLS + 2);       // floats: k, q [TT][DKP]; v [TT][32]; decay, beta [TT]
+  __shared__ float sm[2 * STAGE];
+  const int b = blockIdx.z, h = blockIdx.y, tid = threadIdx.x;
+  const int c = tid / NS, s = tid % NS;
+  const int j0 = blockIdx.x * DELTA_COLS, j = j0 + c;
   const bool col_ok = j < dv;
   const int kvh = h / (H / G);
   float* st = state + (((size_t)slots[b] * H + h) * dk) * dv + (col_ok ? j : 0);
@@ -69,35 +81,75 @@ delta_rule_kernel(const float* __restrict__ qkv, int ld, int q_off, int k_off, i
     const int r = s + i * NS;
     S[i] = (!fresh && col_ok && r < dk) ? st[(size_t)r * dv] : 0.f;
   }
+  if (dk != DKP || dv - j0 < DELTA_COLS)                             // rows past dk and columns past dv stay zero
+    for (int i = tid; i < 2 * STAGE; i += NT) sm[i] = 0.f;
+  __syncthreads();
   const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
-  for (int t = t0; t < t1; t++) {
-    const float* row = qkv + (size_t)t * ld;
-    const float* kr = row + k_off + kvh * dk;
-    const float* qr = row + q_off + kvh * dk;
-    const float g = decay[(size_t)t * H + h], bt = beta[(size_t)t * H + h];
-    const float v = col_ok ? row[v_off + h * dv + j] : 0.f;
-    float kk[DKQ];
-    float dot = 0.f;
-#pragma unroll
-    for (int i = 0; i < DKQ; i++) {
-      const int r = s + i * NS;
-      kk[i] = r < dk ? kr[r] : 0.f;
-      dot = fmaf(S[i], kk[i], dot);
+  const int n_tiles = (t1 - t0 + TT - 1) / TT;
+  const int n_cols = min(DELTA_COLS, dv - j0);
+  auto load = [&](int tile, int buf) {
+    float* base = sm + buf * STAGE;
+    const int ta = t0 + tile * TT, nt = min(TT, t1 - ta);
+    for (int i = tid; i < nt * dk; i += NT) {
+      const int tt = i / dk, r = i - tt * dk;
+      const float* row = qkv + (size_t)(ta + tt) * ld;
+      delta_cp4(base + tt * DKP + r, row + k_off + kvh * dk + r);
+      delta_cp4(base + TT * DKP + tt * DKP + r, row + q_off + kvh * dk + r);
     }
-#pragma unroll
-    for (int o = 1; o < NS; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    const float u = bt * (v - g * dot);                 // (g S)^T k = g (S^T k)
-    float out = 0.f;
-#pragma unroll
-    for (int i = 0; i < DKQ; i++) {
-      const int r = s + i * NS;
-      S[i] = fmaf(kk[i], u, g * S[i]);
-      out = fmaf(S[i], r < dk ? qr[r] : 0.f, out);
+    for (int i = tid; i < nt * n_cols; i += NT) {
+      const int tt = i / n_cols, cc = i - tt * n_cols;
+      delta_cp4(base + 2 * TT * DKP + tt * DELTA_COLS + cc, qkv + (size_t)(ta + tt) * ld + v_off + h * dv + j0 + cc);
     }
+    if (tid < nt) {
+      delta_cp4(base + 2 * TT * DKP + TT * DELTA_COLS + tid, decay + (size_t)(ta + tid) * H + h);
+      delta_cp4(base + 2 * TT * DKP + TT * DELTA_COLS + TT + tid, beta + (size_t)(ta + tid) * H + h);
+    }
+  };
+  if (n_tiles > 0) load(0, 0);
+  delta_cp_commit();
+  for (int tile = 0; tile < n_tiles; tile++) {
+    const int buf = tile & 1;
+    if (tile + 1 < n_tiles) load(tile + 1, buf ^ 1);
+    delta_cp_commit();
+    delta_cp_wait<1>();
+    __syncthreads();
+    const float* ks = sm + buf * STAGE;
+    const float* qs = ks + TT * DKP;
+    const float* vs = qs + TT * DKP;
+    const float* gs = vs + TT * DELTA_COLS;
+    const float* bs = gs + TT;
+    const int ta = t0 + tile * TT, nt = min(TT, t1 - ta);
+    for (int tt = 0; tt < nt; tt++) {
+      const float g = gs[tt], bt = bs[tt], v = vs[tt * DELTA_COLS + c];
+      float kk[DKQ];
+      float d0 = 0.f, d1 = 0.f;
 #pragma unroll
-    for (int o = 1; o < NS; o <<= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
-    if (s == 0 && col_ok) y[(size_t)t * ldy + h * dv + j] = out;
+      for (int i = 0; i < DKQ; i += 2) {
+        kk[i] = ks[tt * DKP + s + i * NS];
+        kk[i + 1] = ks[tt * DKP + s + (i + 1) * NS];
+        d0 = fmaf(S[i], kk[i], d0);
+        d1 = fmaf(S[i + 1], kk[i + 1], d1);
+      }
+      float dot = d0 + d1;
+#pragma unroll
+      for (int o = 1; o < NS; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      const float u = bt * (v - g * dot);               // (g S)^T k = g (S^T k)
+      float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < DKQ; i += 2) {
+        S[i] = fmaf(kk[i], u, g * S[i]);
+        S[i + 1] = fmaf(kk[i + 1], u, g * S[i + 1]);
+        o0 = fmaf(S[i], qs[tt * DKP + s + i * NS], o0);
+        o1 = fmaf(S[i + 1], qs[tt * DKP + s + (i + 1) * NS], o1);
+      }
+      float out = o0 + o1;
+#pragma unroll
+      for (int o = 1; o < NS; o <<= 1) out += __shfl_xor_sync(0xffffffffu, out, o);
+      if (s == 0 && col_ok) y[(size_t)(ta + tt) * ldy + h * dv + j] = out;
+    }
+    __syncthreads();                                    // the tile's buffer is free for the tile after the next
   }
+  delta_cp_wait<0>();
   if (col_ok) {
 #pragma unroll
     for (int i = 0; i < DKQ; i++) {
@@ -106,6 +158,10 @@ delta_rule_kernel(const float* __restrict__ qkv, int ld, int q_off, int k_off, i
     }
   }
 }
+
+static int g_delta_split = 0;
+// Fixes how many threads share a column of the state (4 or 8; 0: chosen from the key size); for tests and comparisons.
+extern "C" void tlc_delta_rule_split(int threads) { g_delta_split = (threads == 4 || threads == 8) ? threads : 0; }
 
 // qkv float [T, ld]: the normalised queries (G heads of dk) at q_off, keys at k_off, values (H heads of dv) at v_off;
 // beta, decay float [T, H]; state float [n_slots, H, dk, dv], updated in place (a sequence at position 0 starts from
@@ -117,13 +173,17 @@ extern "C" int tlc_delta_rule(const float* qkv, int ld, int q_off, int k_off, in
   TLC_REQUIRE(H >= 1 && G >= 1 && H % G == 0 && H <= 65535 && B <= 65535, "delta_rule: %d heads over %d query/key heads, %d sequences", H, G, B);
   TLC_REQUIRE(dk >= 1 && dk <= 256 && dv >= 1, "delta_rule: keys of %d values exceed the kernel's limit of 256", dk);
   const dim3 grid((dv + DELTA_COLS - 1) / DELTA_COLS, H, B);
-#define DELTA_LAUNCH(DKQ, NS)                                                                                               \
-  tlc_launch(delta_rule_kernel<DKQ, NS>, grid, dim3(DELTA_COLS * NS), 0, stream, qkv, ld, q_off, k_off, v_off, beta, decay, state, \
+#define DELTA_LAUNCH(DKQ, NS, TT)                                                                                           \
+  tlc_launch(delta_rule_kernel<DKQ, NS, TT>, grid, dim3(DELTA_COLS * NS), 0, stream, qkv, ld, q_off, k_off, v_off, beta, decay, state, \
              cu_seqlens, slots, start_pos, H, G, dk, dv, y, ldy)
-  if (dk <= 32) DELTA_LAUNCH(8, 4);
-  else if (dk <= 64) DELTA_LAUNCH(16, 4);
-  else if (dk <= 128) DELTA_LAUNCH(32, 4);
-  else DELTA_LAUNCH(32, 8);
+  // threads a column: four, unless told otherwise.  Eight halve a token's chains of multiply-adds and give an SM's
+  // schedulers a second warp, but measured no faster for prompts (2,048 tokens, 16 heads of 128 x 128: 829 against 837
+  // us) and slower for single tokens (38 against 29 us at batch 64: one more round of shuffles)
+  const int ns = g_delta_split ? g_delta_split : 4;
+  if (dk <= 32) { if (ns == 4) DELTA_LAUNCH(8, 4, 16); else DELTA_LAUNCH(4, 8, 16); }
+  else if (dk <= 64) { if (ns == 4) DELTA_LAUNCH(16, 4, 16); else DELTA_LAUNCH(8, 8, 16); }
+  else if (dk <= 128) { if (ns == 4) DELTA_LAUNCH(32, 4, 16); else DELTA_LAUNCH(16, 8, 16); }
+  else DELTA_LAUNCH(32, 8, 8);
 #undef DELTA_LAUNCH
   TLC_CHECK_LAUNCH("delta_rule");
   return 0;

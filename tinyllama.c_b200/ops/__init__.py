@@ -112,6 +112,7 @@ _SIGNATURES = {
     "tlc_qk_rotate_norm": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _f, _vp, _i, _vp]),
     "tlc_gate_mul": (_i, [_vp, _i, _i, _vp, _i, _i, _i, _i, _vp]),
     "tlc_delta_prepare": (_i, [_vp, _i, _i, _i, _i, _i, _f, _f, _vp, _i, _i, _i, _vp, _i, _vp]),
+    "tlc_delta_rule_split": (None, [_i]),
     "tlc_delta_rule": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp]),
     "tlc_moe_down": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
     "tlc_argmax": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
@@ -1089,6 +1090,12 @@ def delta_prepare(qkv: torch.Tensor, q_off: int, k_off: int, G: int, dk: int, l2
         raise KernelError("delta_prepare: float32 tensors, beta contiguous [T, H]")
     _call("tlc_delta_prepare", qkv.data_ptr(), _rows(qkv, "qkv"), int(q_off), int(k_off), int(G), int(dk), float(l2_eps),
           float(q_scale), proj.data_ptr(), _rows(proj, "proj"), int(b_off), int(H), beta.data_ptr(), T, _stream())
+
+
+def delta_rule_split(threads: int) -> None:
+    """Fixes how many threads of the delta rule's kernel share a column of the state (4 or 8; 0: chosen from the key size);
+    for tests and comparisons."""
+    library().tlc_delta_rule_split(int(threads))
 
 
 def delta_rule(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, beta: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
