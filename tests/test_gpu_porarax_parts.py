@@ -161,15 +161,18 @@ def _delta_plain(q, k, v, beta, decay, H, G, dk, dv):
     return o
 
 
+@pytest.mark.parametrize("split", [0, 8, 16])
 @pytest.mark.parametrize("H,G,dk,dv", [(2, 1, 8, 8), (4, 2, 40, 12), (2, 2, 64, 64), (3, 3, 100, 33), (2, 1, 256, 16), (1, 1, 130, 70)])
-def test_delta_rule_keeps_what_was_written_hundreds_of_tokens_back(H, G, dk, dv):
+def test_delta_rule_keeps_what_was_written_hundreds_of_tokens_back(H, G, dk, dv, split, request):
     """Two sequences in one step, then continued in portions and single tokens; decays within 1e-3 of one, and a value
     written at token 3 with a key that later queries repeat: the read-out hundreds of tokens later is mostly that value,
     so a state that is lost, reset, scaled twice or mixed up between sequences, heads or slots shows.  The slots held
     rubbish before (a sequence at position 0 starts from zero whatever its slot holds), and slot 0 is then used again by
     a third sequence."""
+    ops.delta_rule_split(split)                     # threads that share a column group's rows: both shapes of the kernel
+    request.addfinalizer(lambda: ops.delta_rule_split(0))
     g = np.random.default_rng(5)
-    lens, portions = [330, 97], [[200, 1, 1, 64, 64], [90, 1, 1, 3, 2]]
+    lens, portions = [330, 97], [[203, 1, 1, 61, 64], [90, 1, 1, 3, 2]]
     n_slots = 3
     state = torch.full((n_slots, H, dk, dv), 3.0, device="cuda")
 

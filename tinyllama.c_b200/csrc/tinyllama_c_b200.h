@@ -295,10 +295,10 @@ int tlc_gate_mul(void* x, int dtype, int ldx, const float* gate, int ldg, int n,
  * v_off, beta and decay float [T, H]; y [T, ldy] float receives o (head h at column h * dv). */
 int tlc_delta_prepare(float* qkv, int ld, int q_off, int k_off, int G, int dk, float l2_eps, float q_scale, const float* proj,
                       int ldp, int b_off, int H, float* beta, int T, cudaStream_t stream);
-void tlc_delta_rule_split(int threads);   /* threads that share a column of the state: 4 or 8 (0: chosen); for tests */
+void tlc_delta_rule_split(int threads);   /* threads that share the rows of a column group: 8 or 16 (0: chosen); for tests */
 int tlc_delta_rule(const float* qkv, int ld, int q_off, int k_off, int v_off, const float* beta, const float* decay,
-                   float* state, const int* cu_seqlens, const int* slots, const int* start_pos, int B, int H, int G, int dk,
-                   int dv, float* y, int ldy, cudaStream_t stream);
+                   float* state, const int* cu_seqlens, const int* slots, const int* start_pos, int B, int T, int H, int G,
+                   int dk, int dv, float* y, int ldy, cudaStream_t stream);
 
 /* ---- mixture of experts (moe.cu) ------------------------------------------------------------------------
  * tlc_moe_route: logits float [T, ld] (E columns) -> per token its `top` experts by descending logit (lowest index

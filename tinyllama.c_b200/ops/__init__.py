@@ -113,7 +113,7 @@ _SIGNATURES = {
     "tlc_gate_mul": (_i, [_vp, _i, _i, _vp, _i, _i, _i, _i, _vp]),
     "tlc_delta_prepare": (_i, [_vp, _i, _i, _i, _i, _i, _f, _f, _vp, _i, _i, _i, _vp, _i, _vp]),
     "tlc_delta_rule_split": (None, [_i]),
-    "tlc_delta_rule": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp]),
+    "tlc_delta_rule": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _vp]),
     "tlc_moe_down": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
     "tlc_argmax": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "tlc_sample": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _f, _f, _f, _i, _f, _f, _vp, _vp]),
@@ -1093,8 +1093,8 @@ def delta_prepare(qkv: torch.Tensor, q_off: int, k_off: int, G: int, dk: int, l2
 
 
 def delta_rule_split(threads: int) -> None:
-    """Fixes how many threads of the delta rule's kernel share a column of the state (4 or 8; 0: chosen from the key size);
-    for tests and comparisons."""
+    """Fixes how many threads of the delta rule's kernel share the rows of a column group of the state (8 or 16; 0:
+    chosen: 16 for prompts, 8 for single-token steps); for tests and comparisons."""
     library().tlc_delta_rule_split(int(threads))
 
 
@@ -1115,5 +1115,5 @@ def delta_rule(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, beta: torc
         raise KernelError("delta_rule: y must be float32")
     ldy = _out_rows(y, T, H * dv, "delta_rule")
     _call("tlc_delta_rule", qkv.data_ptr(), _rows(qkv, "qkv"), int(q_off), int(k_off), int(v_off), beta.data_ptr(), decay.data_ptr(),
-          state.data_ptr(), step.cu_seqlens.data_ptr(), step.slots.data_ptr(), step.start_pos.data_ptr(), step.n_seqs, int(H), int(G),
-          int(dk), int(dv), y.data_ptr(), ldy, _stream())
+          state.data_ptr(), step.cu_seqlens.data_ptr(), step.slots.data_ptr(), step.start_pos.data_ptr(), step.n_seqs, T, int(H),
+          int(G), int(dk), int(dv), y.data_ptr(), ldy, _stream())
