@@ -135,11 +135,12 @@ def test_rotation_of_pairs_and_unit_rms(dim, stride, rot, interleaved):
         assert np.array_equal(got[:, :lead], x[:, :lead].astype(np.float64)) and np.array_equal(got[:, -3:], x[:, -3:].astype(np.float64))
 
 
+@pytest.mark.parametrize("pad", [9, 12])            # (12: rows of the gate on 16-byte boundaries, four elements a thread)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_output_gate(dtype):
+def test_output_gate(dtype, pad):
     g = np.random.default_rng(4)
     T, n = 7, 52
-    x, gate = draw(g, (T, n), 1.0, dtype), g.standard_normal((T, n + 9)).astype(np.float32) * 3.0
+    x, gate = draw(g, (T, n), 1.0, dtype), g.standard_normal((T, n + pad)).astype(np.float32) * 3.0
     for kind, fn in (("sigmoid", plain.sigmoid), ("silu", plain.silu)):
         buf, gd = dev(x, DT[dtype]), dev(gate)
         ops.gate_mul(buf, gd[:, 4:4 + n], kind)

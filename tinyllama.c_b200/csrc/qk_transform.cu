@@ -58,17 +58,51 @@ extern "C" int tlc_qk_rotate_norm(float* qkv, int ld, int q_off, int k_off, int 
   return 0;
 }
 
-template <typename TX, bool QUICK>
+// Four neighbouring elements a thread (n a multiple of 4, rows that start on 16-byte boundaries of the gate and 8-byte
+// (bfloat16) or 16-byte (float) boundaries of x), else one.
+template <typename TX, bool QUICK, int VEC>
 __global__ void __launch_bounds__(256)
 gate_mul_kernel(TX* __restrict__ x, int ldx, const float* __restrict__ gate, int ldg, int n, int T, int act) {
   tlc_pdl(x, gate);
+  const int per_row = n / VEC;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (long long)T * n) return;
-  const int t = (int)(i / n), c = (int)(i - (long long)t * n);
-  const float g = gate[(size_t)t * ldg + c];
-  const float s = QUICK ? __fdividef(1.0f, 1.0f + __expf(-g)) : 1.0f / (1.0f + expf(-g));
+  if (i >= (long long)T * per_row) return;
+  const int t = (int)(i / per_row), c = (int)(i - (long long)t * per_row) * VEC;
+  float g[VEC], v[VEC];
   TX* p = x + (size_t)t * ldx + c;
-  *p = from_f32<TX>(to_f32(*p) * (act == 1 ? g * s : s));
+  if (VEC == 4) {
+    const float4 g4 = *reinterpret_cast<const float4*>(gate + (size_t)t * ldg + c);
+    g[0] = g4.x; g[1] = g4.y; g[2] = g4.z; g[VEC - 1] = g4.w;
+    if (sizeof(TX) == 2) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(p);
+      const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+      v[0] = __low2float(lo); v[1] = __high2float(lo); v[2] = __low2float(hi); v[VEC - 1] = __high2float(hi);
+    } else {
+      const float4 x4 = *reinterpret_cast<const float4*>(p);
+      v[0] = x4.x; v[1] = x4.y; v[2] = x4.z; v[VEC - 1] = x4.w;
+    }
+  } else {
+    g[0] = gate[(size_t)t * ldg + c];
+    v[0] = to_f32(*p);
+  }
+#pragma unroll
+  for (int e = 0; e < VEC; e++) {
+    const float s = QUICK ? __fdividef(1.0f, 1.0f + __expf(-g[e])) : 1.0f / (1.0f + expf(-g[e]));
+    v[e] *= act == 1 ? g[e] * s : s;
+  }
+  if (VEC == 4) {
+    if (sizeof(TX) == 2) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[VEC - 1]);
+      uint2 raw;
+      raw.x = *reinterpret_cast<unsigned*>(&lo);
+      raw.y = *reinterpret_cast<unsigned*>(&hi);
+      *reinterpret_cast<uint2*>(p) = raw;
+    } else {
+      *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[VEC - 1]);
+    }
+  } else {
+    *p = from_f32<TX>(v[0]);
+  }
 }
 
 // x[t, c] *= sigmoid(gate[t, c]) (act 0) or silu(gate[t, c]) (act 1); x [T, n] of `dtype` with row stride ldx, gate float
@@ -76,11 +110,18 @@ gate_mul_kernel(TX* __restrict__ x, int ldx, const float* __restrict__ gate, int
 extern "C" int tlc_gate_mul(void* x, int dtype, int ldx, const float* gate, int ldg, int n, int T, int act, cudaStream_t stream) {
   if (T == 0 || n == 0) return 0;
   TLC_REQUIRE(act == 0 || act == 1, "gate_mul: unknown gate %d", act);
-  const long long total = (long long)T * n;
+  const size_t esz = dtype == TLC_BF16 ? 2 : 4;
+  const bool vec = n % 4 == 0 && ldg % 4 == 0 && (uintptr_t)gate % 16 == 0 && (ldx * esz) % (4 * esz) == 0 && (uintptr_t)x % (4 * esz) == 0;
+  const long long total = (long long)T * (vec ? n / 4 : n);
   const dim3 grid((unsigned)((total + 255) / 256));
-  if (dtype == TLC_BF16) tlc_launch(gate_mul_kernel<__nv_bfloat16, true>, grid, dim3(256), 0, stream, (__nv_bfloat16*)x, ldx, gate, ldg, n, T, act);
-  else if (dtype == TLC_F32) tlc_launch(gate_mul_kernel<float, false>, grid, dim3(256), 0, stream, (float*)x, ldx, gate, ldg, n, T, act);
-  else return tlc_fail(-1, "gate_mul: unknown dtype code %d", dtype);
+  if (dtype != TLC_BF16 && dtype != TLC_F32) return tlc_fail(-1, "gate_mul: unknown dtype code %d", dtype);
+  if (dtype == TLC_BF16) {
+    if (vec) tlc_launch(gate_mul_kernel<__nv_bfloat16, true, 4>, grid, dim3(256), 0, stream, (__nv_bfloat16*)x, ldx, gate, ldg, n, T, act);
+    else tlc_launch(gate_mul_kernel<__nv_bfloat16, true, 1>, grid, dim3(256), 0, stream, (__nv_bfloat16*)x, ldx, gate, ldg, n, T, act);
+  } else {
+    if (vec) tlc_launch(gate_mul_kernel<float, false, 4>, grid, dim3(256), 0, stream, (float*)x, ldx, gate, ldg, n, T, act);
+    else tlc_launch(gate_mul_kernel<float, false, 1>, grid, dim3(256), 0, stream, (float*)x, ldx, gate, ldg, n, T, act);
+  }
   TLC_CHECK_LAUNCH("gate_mul");
   return 0;
 }
