@@ -124,3 +124,39 @@ PORARAX_B = dict(architecture="Porarax", vocab=97, width=44, norm=dict(eps=1e-6)
 ])
 
 PORARAX = {"PA": PORARAX_A, "PB": PORARAX_B}
+
+
+def porarax_random(seed: int) -> dict:
+    """A Porarax configuration drawn from `seed`: 3 to 6 layers of any kind in any order, readers of earlier latents,
+    head counts, sizes, windows, taps, experts and constants all drawn (small sizes: the plain model is slow)."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    pick = lambda *v: v[int(rng.integers(len(v)))]
+    layers, owners = [], []
+    for i in range(int(rng.integers(3, 7))):
+        kind = pick("latent_attention", "attention", "delta")
+        if kind == "latent_attention":
+            dim = pick(8, 16, 24, 32)
+            if owners and rng.random() < 0.5:
+                src = pick(*owners)
+                rank, extra = layers[src]["mixer"]["kv_rank"], dict(kv_from=src)
+            else:
+                rank, extra = pick(16, 20, 32, 48, 80), {}
+                owners.append(i)
+            layer = dict(type=kind, mixer=dict(heads=pick(1, 2, 3, 4, 6), dim=dim, vdim=pick(8, 12, 16, 32), kv_rank=rank,
+                                               q_rank=pick(8, 20, 32, 40), scale=float(dim ** -0.5 * rng.uniform(0.5, 2.0)),
+                                               mask=dict(size=pick(1, 3, 63, 64, 65, 90, 128, 1000)), **extra))
+        elif kind == "attention":
+            kv, dim = pick(1, 2, 3), pick(16, 24, 32, 64, 128)
+            layer = dict(type=kind, mixer=dict(heads=kv * pick(1, 2, 4, 9), kv_heads=kv, dim=dim, vdim=pick(dim, dim, 16, 40, 64),
+                                               scale=float(dim ** -0.5 * rng.uniform(0.5, 2.0)),
+                                               rot=dict(base=pick(50.0, 10000.0, 500000.0), dims=pick(0, 2, dim // 4 * 2, dim))))
+        else:
+            kv = pick(1, 2, 3)
+            layer = dict(type=kind, mixer=dict(heads=kv * pick(1, 2, 3), kv_heads=kv, dim=pick(8, 20, 32, 64, 72, 136), vdim=pick(8, 12, 32, 40),
+                                               conv=pick(1, 2, 3, 4, 6)))
+        experts = pick(1, 2, 3, 5, 8, 33)
+        layer["mlp"] = None if rng.random() < 0.15 else _p_moe(experts, int(rng.integers(1, min(experts, 4) + 1)), pick(8, 12, 24, 40),
+                                                               pick(0.5, 2.0, 7.0))
+        layers.append(layer)
+    return dict(architecture="Porarax", vocab=pick(50, 131, 300), width=pick(32, 44, 64, 96), norm=dict(eps=pick(1e-5, 1e-6)), layers=layers)
