@@ -417,7 +417,7 @@ def porarax_work(cfg, batch, context, T):
             G = m["kv_heads"]
             fixed += (2 * G * dk + 2 * H * dv + 2 * H) * D + D * H * dv
             cache_bytes += batch * H * dk * dv * 4                    # the state, 32-bit
-            mix_flops += 6.0 * H * dk * dv * T                        # S^T k, k u^T, S^T q
+            mix_flops += 6.0 * H * dk * dv * T                        # the prediction M^T k, the write k w^T, the read-out M^T q
         mlp = layer["mlp"]
         E, top, F = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"]
         fixed += E * D

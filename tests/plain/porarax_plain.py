@@ -6,7 +6,7 @@ everything in float64 except the rotary angle, which is the float32 product of p
 are BUILT per head and per token (the engine never builds the latent layers' keys), the delta rule walks token by token,
 and every expert is applied to its tokens one at a time.
 
-Notation: D model width, T tokens of one sequence.  A layer is  h = n(x);  x <- x + mixer(h) + ff(h)  with
+Notation: D model width, T tokens of one sequence.  A layer is  h = n(x);  x <- mixer(h) + ff(h) + x  with
 n(x) = x / sqrt(mean(x^2) + eps) * w.  `rnd` models a bfloat16 engine: it is applied where such an engine must round
 (inputs of matrix products, cached rows); the identity gives exact arithmetic.
 """
@@ -150,7 +150,7 @@ def delta(h, W, p, m, eps, rnd=_same):
 
 # ---- mixture of experts -----------------------------------------------------------------------------------------------
 def route(z, top):
-    """z [E] logits -> (chosen experts by descending logit, lowest index first on ties; softmax over the chosen)."""
+    """z [E] logits -> (experts picked by descending logit, lowest index first on ties; softmax restricted to the picked)."""
     order = sorted(range(len(z)), key=lambda e: (-z[e], e))[:top]
     zz = np.array([z[e] for e in order])
     w = np.exp(zz - zz.max())

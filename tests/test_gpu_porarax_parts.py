@@ -2,8 +2,8 @@
 attention over a window with one key that decides the result just inside and just outside the window, at page borders,
 at the query's own position (both kernels, prompts' portions and single tokens, keys cut into ranges); the rotation of
 neighbouring pairs with the unit-RMS norm; the output gate; the delta rule with a state that barely decays, so that
-what was written hundreds of tokens back still decides the output, across steps, with a slot used again; routing by the
-softmax over the chosen logits with a bias and exact ties; the clamped experts with both clamps at work.
+what was written hundreds of tokens back still decides the output, across steps, with a slot used again; routing by a
+softmax restricted to the picked logits, with a bias and exact ties; the clamped experts with both clamps at work.
 """
 import numpy as np
 import pytest

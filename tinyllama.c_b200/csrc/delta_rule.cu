@@ -1,13 +1,14 @@
 // The gated delta rule: a recurrence over tokens whose state is a matrix per head, corrected towards every new
 // (key, value) pair instead of merely summing them.
 //
-// Per head, with the token's unit-length key k and query q (dk values), value v (dv values), write strength beta in (0, 1)
-// and decay g in (0, 1], and the state S [dk, dv] (32-bit, zero at position 0, kept per sequence between steps):
-//   S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
-// in this order, so the read-out sees the token's own write.  Query and key heads may be shared by several value heads
-// (head h uses q/k head h / (H / G)).
+// Per head, with the token's unit-length key k and query q (dk values), value v (dv values), write strength b in (0, 1)
+// and decay a in (0, 1], and the state M [dk, dv] (32-bit, zero at position 0, kept per sequence between steps): the state
+// is decayed, asked what it would return for the new key (the prediction p), corrected by the write w, and read:
+//   M <- a M;   p = M^T k;   w = b (v - p);   M <- M + k w^T;   r = M^T q
+// (the read-out comes last: it already contains what this token wrote; in the code M is S, w is u, a is g, b is bt).
+// Several value heads may share a query/key head (value head i reads query/key head i / (H / G)).
 //
-// Column j of S depends on column j alone: u_j = beta (v_j - S[:, j] . k), S[:, j] <- g S[:, j] + k u_j, o_j = S[:, j] . q.
+// Column j of M depends on column j alone: w_j = b (v_j - M[:, j] . k), M[:, j] <- a M[:, j] + k w_j, r_j = M[:, j] . q.
 // So a group of NS threads (neighbouring lanes) owns four columns: each holds DKQ rows of them in registers; the group
 // walks the sequence's rows of this step in order and joins its partial dot products by shuffles.  A block takes 32
 // columns of one (sequence, head).  Everything is 32-bit.
@@ -164,7 +165,7 @@ delta_rule_kernel(const float* __restrict__ qkv, int ld, int q_off, int k_off, i
       for (int o = 1; o < NS; o <<= 1)
 #pragma unroll
         for (int cc = 0; cc < CT; cc++) d[cc] += __shfl_xor_sync(0xffffffffu, d[cc], o);
-      float u[CT];                                      // (g S)^T k = g (S^T k)
+      float u[CT];                                      // the decayed state's prediction: (a M)^T k = a (M^T k)
       u[0] = bt * (vv.x - g * d[0]); u[1] = bt * (vv.y - g * d[1]); u[2] = bt * (vv.z - g * d[2]); u[3] = bt * (vv.w - g * d[3]);
       float out[CT];
 #pragma unroll
@@ -205,7 +206,7 @@ extern "C" void tlc_delta_rule_split(int threads) { g_delta_split = (threads == 
 
 // qkv float [T, ld]: the normalised queries (G heads of dk) at q_off, keys at k_off, values (H heads of dv) at v_off;
 // beta, decay float [T, H]; state float [n_slots, H, dk, dv], updated in place (a sequence at position 0 starts from
-// zero whatever its slot holds); y float [T, ldy] receives o, head h at column h * dv.  B sequences, T rows in all.
+// zero whatever its slot holds); y float [T, ldy] receives the read-outs, head h at column h * dv.  B sequences, T rows in all.
 extern "C" int tlc_delta_rule(const float* qkv, int ld, int q_off, int k_off, int v_off, const float* beta, const float* decay,
                               float* state, const int* cu_seqlens, const int* slots, const int* start_pos, int B, int T, int H,
                               int G, int dk, int dv, float* y, int ldy, cudaStream_t stream) {

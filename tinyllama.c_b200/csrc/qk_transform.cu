@@ -3,8 +3,8 @@
 //
 // tlc_qk_rotate_norm works on the 32-bit projection in place, a warp per (row, head), query heads and key heads alike:
 // it turns the pairs of the first `rot` dimensions of a head by angle = position * inv_freq[i] (pairs (2i, 2i+1) with
-// interleaved != 0, else (i, i + rot/2); dimensions past `rot` pass unchanged) and then, with norm_eps >= 0, divides the
-// head by its root mean square over its `dim` dimensions, x / sqrt(mean(x^2) + eps), without a weight.  Heads may lie
+// interleaved != 0, else (i, i + rot/2); dimensions past `rot` pass unchanged) and then, with norm_eps >= 0, scales the
+// head to unit root mean square over its `dim` dimensions, x / sqrt(mean(x^2) + eps), without a weight.  Heads may lie
 // `stride` >= dim values apart (a mixer whose values are wider than its keys pads the heads; the padding stays zero).
 // Everything is 32-bit; the kernels that store keys and values then need not rotate.
 //

@@ -32,7 +32,7 @@
 #define TLC_ACT_GELU_TANH 1  /* 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) */
 #define TLC_ACT_SWISH_CLAMPED 2 /* experts only: g = min(g, limit), u = clamp(u, -limit, limit): g sigmoid(alpha g) (u + 1) */
 #define TLC_ROUTE_SIGMOID 0  /* a chosen expert's weight is the sigmoid of its logit */
-#define TLC_ROUTE_SOFTMAX 1  /* the chosen experts' weights are the softmax over their logits alone */
+#define TLC_ROUTE_SOFTMAX 1  /* the chosen experts' weights are the softmax restricted to their own logits */
 
 #ifdef __cplusplus
 extern "C" {
@@ -288,11 +288,12 @@ int tlc_qk_rotate_norm(float* qkv, int ld, int q_off, int k_off, int H, int KV, 
 int tlc_gate_mul(void* x, int dtype, int ldx, const float* gate, int ldg, int n, int T, int act, cudaStream_t stream);
 
 /* ---- gated delta rule (delta_rule.cu) -------------------------------------------------------------------
- * Per head: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with S [dk, dv] float per (slot, head) in state
+ * Per head: M <- a M; w = b (v - M^T k); M <- M + k w^T; r = M^T q (a the decay, b the write strength `beta`), with M
+ * [dk, dv] float per (slot, head) in state
  * [n_slots, H, dk, dv] (zero at position 0).  tlc_delta_prepare normalises, in place in qkv [T, ld] float, the G query
  * heads at q_off (x / sqrt(sum x^2 + l2_eps) * q_scale) and the G key heads at k_off (the same without the scale), and
  * writes beta[t, h] = sigmoid(proj[t, b_off + h]).  tlc_delta_rule walks every sequence's rows: values (H heads of dv) at
- * v_off, beta and decay float [T, H]; y [T, ldy] float receives o (head h at column h * dv). */
+ * v_off, beta and decay float [T, H]; y [T, ldy] float receives the read-outs (head h at column h * dv). */
 int tlc_delta_prepare(float* qkv, int ld, int q_off, int k_off, int G, int dk, float l2_eps, float q_scale, const float* proj,
                       int ldp, int b_off, int H, float* beta, int T, cudaStream_t stream);
 void tlc_delta_rule_split(int threads);   /* threads that share the rows of a column group: 8 or 16 (0: chosen); for tests */
@@ -302,8 +303,8 @@ int tlc_delta_rule(const float* qkv, int ld, int q_off, int k_off, int v_off, co
 
 /* ---- mixture of experts (moe.cu) ------------------------------------------------------------------------
  * tlc_moe_route: logits float [T, ld] (E columns) -> per token its `top` experts by descending logit (lowest index
- * first on ties) in ids [T*top] with weights wts = sigmoid(logit) (mode TLC_ROUTE_SIGMOID) or the softmax over the
- * chosen logits (TLC_ROUTE_SOFTMAX); order [T*top] lists the pairs (t * top + k) sorted
+ * first on ties) in ids [T*top] with weights wts = sigmoid(logit) (mode TLC_ROUTE_SIGMOID) or a softmax restricted to
+ * the picked logits (TLC_ROUTE_SOFTMAX); order [T*top] lists the pairs (t * top + k) sorted
  * by expert, offsets [E+1] every expert's first sorted position, tile_off [E+1] its first tile of tile_rows sorted rows
  * (32 for tlc_moe_gate_up / tlc_moe_down; 32 or 64 for tlc_moe_experts_mma, which is told the same number). */
 int tlc_moe_route(const float* logits, int ld, int T, int E, int top, int mode, int* ids, float* wts, int* order, int* offsets,

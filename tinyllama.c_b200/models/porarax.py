@@ -1,12 +1,12 @@
 """Porarax: per layer one norm, then a mixer and a mixture-of-experts feed-forward side by side on the normed input,
 
-    h = norm1(x);    x <- x + mixer(h) + ff(h)
+    h = norm1(x);    x <- mixer(h) + ff(h) + x
 
 with three kinds of mixer: latent attention without positions over a sliding window (queries through a latent of their
 own; a layer may attend over the latents ANOTHER layer cached), grouped-query attention with a partial rotation of
 neighbouring pairs, unit-RMS queries and keys and a sigmoid output gate, and the gated delta rule.  The experts' router
-adds a bias to its logits and weighs the chosen experts by the softmax over their logits alone; an expert is
-W_down (g * sigmoid(1.702 g) * (u + 1)) with g = min(W_gate h, limit) and u = W_up h held within +-limit.  The head is the
+adds a bias to its logits and weighs the picked experts by a softmax restricted to their own logits; an expert is
+W_down ((u + 1) * g / (1 + exp(-1.702 g))) with g = min(W_gate h, limit) and u = W_up h held within +-limit.  The head is the
 embedding table.  This file only turns a PoraraxConfig into data: one LayerSpec per layer, the run order (which entry
 reads whose cached latents), and the tensor names ('l<i>.' + norm1, mix.*, mlp.*; 'embed'; 'final.norm').
 """

@@ -983,7 +983,7 @@ MOE_ACTS = dict(GLU_ACTS, swish_clamped=2)
 
 def moe_route(logits: torch.Tensor, n_experts: int, top: int, tile_rows: int = 32, weights: str = "sigmoid"):
     """Routing of every row of logits (float32 [T, >= E], the first E columns): returns (ids [T*top] int32, weights
-    [T*top] float32 = sigmoid of the chosen logits, or with weights "softmax" the softmax over the chosen logits alone,
+    [T*top] float32 = sigmoid of the chosen logits, or with weights "softmax" a softmax restricted to the picked logits,
     order [T*top], offsets [E+1], tile_off [E+1], tile_rows) as tlc_moe_route describes them."""
     if weights not in ROUTE_WEIGHTS:
         raise KernelError(f"moe_route: unknown weighting '{weights}'; known: {sorted(ROUTE_WEIGHTS)}")
@@ -1101,7 +1101,8 @@ def delta_rule_split(threads: int) -> None:
 def delta_rule(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, beta: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
                step, y: torch.Tensor, H: int, G: int, dk: int, dv: int) -> None:
     """The gated delta rule over every sequence's rows of the step, from its slot's state [n_slots, H, dk, dv] float32
-    (zero at position 0; updated in place): S <- g S; u = beta (v - S^T k); S <- S + k u^T; y = S^T q.  qkv float32
+    (zero at position 0; updated in place): M <- a M; w = b (v - M^T k); M <- M + k w^T; y = M^T q (a the decay, b the
+    write strength `beta`).  qkv float32
     [T, *] holds the prepared queries and keys (G heads of dk) and the values (H heads of dv); beta, decay float32 [T, H];
     y float32 [T, H*dv]."""
     _gpu(qkv, beta, decay, state, y)

@@ -87,7 +87,7 @@ class MoEFeedForward(Part):
     of the token's choices: a token's result does not depend on what else is in the batch.
 
     Other routers and experts, by constructor arguments: a bias on the router's logits (router_bias_name); weights that are
-    the softmax over the chosen logits alone (weights="softmax"); the weight applied to what the expert returns instead of
+    a softmax restricted to the picked logits (weights="softmax"); the weight applied to what the expert returns instead of
     to what it is fed (weight_on="output": sum_e s_e expert_e(h); the down product is linear, so the weight multiplies the
     32-bit activation); the activation act="swish_clamped": with g = min(W_gate h, limit) and u = W_up h held within
     +-limit, g * sigmoid(alpha g) * (u + 1)."""

@@ -9,7 +9,7 @@ keys and the output have no counterpart there; they fold into the projections.
 Options beyond that, each a constructor argument: tensor names of one's own; a score scale other than
 1/sqrt(head size); values of another size than the keys (the narrower of the two is padded with zero rows of
 its projection, so that the kernels see one head size); a rotation of neighbouring pairs (2i, 2i+1); queries and
-keys divided by their root mean square per head after the rotation (no weight); and an output gate, the
+keys scaled to unit root mean square per head after the rotation (no weight); and an output gate, the
 concatenated heads times the sigmoid of one more projection of the mixer's input.  A rotation of neighbours and
 the norm run as one kernel on the 32-bit projection before keys and values are stored.
 """

@@ -1,21 +1,23 @@
 """Gated delta-rule mixer: a recurrence whose state is a matrix per head that every token corrects towards its own
 (key, value) pair.
 
-From the mixer's input h: q = W_q h and k = W_k h (G heads of dk values), v = W_v h (H heads of dv values; head i uses
-q/k head i // (H / G)).  Each of q, k, v passes a short causal convolution over time per channel (weights [channels,
-taps], the last tap on the current token, zeros before the sequence's start) and SiLU; q and k then become unit vectors
-per head, x / sqrt(sum(x^2) + l2_eps), the query also times q_scale (dk ** -0.5 unless given).  Per head
-beta = sigmoid(W_b h) and the decay g = exp(-exp(A_log) * softplus(W_a h + dt_bias)), and
+Three projections of the mixer's input h give queries and keys (G heads of dk values each) and values (H heads of dv;
+value head i reads query/key head i // (H / G)).  All three are smoothed along the sequence, channel by channel, by a
+depthwise filter of `taps` weights that ends at the current token (weights [channels, taps], newest tap last; the
+sequence is preceded by zeros), then go through SiLU.  Queries and keys are then scaled to unit length per head,
+x * rsqrt(sum(x^2) + l2_eps), the query further by q_scale (dk ** -0.5 unless given).  Per head the
+write strength b = sigmoid(W_b h) and the decay a = exp(-exp(A_log) * softplus(W_a h + dt_bias)); the state M [dk, dv] is
+decayed, asked what it would return for the new key (the prediction p), corrected by the write w, and read with the query:
 
-    S <- g S;    u = beta (v - S^T k);    S <- S + k u^T;    o = S^T q
+    M <- a M;    p = M^T k;    w = b (v - p);    M <- M + k w^T;    r = M^T q
 
-in this order.  Every head's o is divided by its root mean square over dv, multiplied by a weight [dv] that the heads
-share and by silu(W_g h), and W_o maps the heads' results back.  S [H, dk, dv] and the last taps - 1 inputs of the
-convolution are kept per sequence between steps (32-bit; a sequence at position 0 starts from zeros); everything
-between the projections and the output projection is 32-bit.
+(the read-out comes last: it already contains what this token wrote).  Each head's r gets an RMS norm across its dv
+values with one weight vector [dv] common to all heads, is gated by silu(W_g h), and W_o maps the heads' results back.
+M [H, dk, dv] and the last taps - 1 inputs of the convolution are kept per sequence between steps (32-bit; a sequence
+at position 0 starts from zeros); everything between the projections and the output projection is 32-bit.
 
-The six projections of h are one product.  The convolution (with the decay beside it: dt = softplus(a + dt_bias),
-decay = exp(dt * -exp(A_log))) is the kernel that serves every short convolution of the library.
+The six projections of h are one product.  The convolution (with the decay beside it: dt = softplus(W_a h + dt_bias),
+a = exp(dt * -exp(A_log))) is the kernel that serves every short convolution of the library.
 """
 from __future__ import annotations
 
