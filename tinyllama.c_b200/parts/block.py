@@ -35,6 +35,17 @@ PARALLEL_PROMPT_MIXERS = bool(int(os.environ.get("TLC_PARALLEL_PROMPT_MIXERS", "
 # attention takes 53 us instead of 30, and the part of the scan that runs beside both finds no room and ends
 # as late as the walk did before: 7.51 ms a step either way.  The three kernels fill the SMs between them.
 PROMPT_SIDE_BLOCKS = int(os.environ.get("TLC_PROMPT_SIDE_BLOCKS", "0"))
+# A feed-forward that runs beside the mixers on their normed input (a parallel layer) and can hand over its terms
+# (forward_parts / add_parts): in one-token steps the two are chains of short kernels and run on two streams; the terms are
+# added into the residual stream after the mixers' outputs, on the current stream, so the order of the sums is fixed.
+# TLC_PARALLEL_FFN=1 (the default) puts the MIXERS on a side stream of high priority and the feed-forward on the current
+# one, 2 the feed-forward on the side stream, 0 runs it after the mixers.  Measured with four layers of experts beside
+# latent attention, attention and a delta rule at width 2048: a step at batch 8 0.654 ms (0), 0.577 (2), 0.543 (1); at
+# batch 64 0.957, 0.857, 0.864.  A prompt of 2,048 tokens gains nothing (3.89 ms one after the other, 3.95 and 4.09 side
+# by side: the experts' products fill the GPU by themselves and slow the mixers' kernels beside them), so prompts run
+# one after the other unless TLC_PARALLEL_FFN_PROMPTS=1.
+PARALLEL_FFN = int(os.environ.get("TLC_PARALLEL_FFN", "1"))
+PARALLEL_FFN_PROMPTS = bool(int(os.environ.get("TLC_PARALLEL_FFN_PROMPTS", "0")))
 
 
 _streams = {}
@@ -196,6 +207,41 @@ class Block(Part):
         joint = scratch_buf("block.joint", (x32.shape[0], self.fused_out.in_features), self.dtype, x32.device)
         return joint, [joint[:, off:off + n] for off, n in self.out_offsets]
 
+    def _beside(self, x32: torch.Tensor, step: StepInfo):
+        """Whether this layer's feed-forward runs beside its mixers on two streams in this step."""
+        return bool(self.parallel_ffn and PARALLEL_FFN and x32.is_cuda and (step.max_new == 1 or PARALLEL_FFN_PROMPTS)
+                    and hasattr(self.ffn, "forward_parts") and hasattr(self.ffn, "add_parts"))
+
+    def _two_branches(self, normed: torch.Tensor, x32: torch.Tensor, run_mixers) -> None:
+        """A parallel layer on two streams (under stream capture: two branches of the graph): the mixers, which add
+        their outputs into the residual stream, and the feed-forward's terms; the terms are added after the branches have
+        met, on the current stream, so the order of the sums is fixed.  run_mixers(): launches the mixers on whatever
+        stream is current."""
+        main = _current_stream(x32.device)
+        if not hasattr(self, "_ffn_side"):
+            least, greatest = torch.cuda.Stream.priority_range() if hasattr(torch.cuda.Stream, "priority_range") else (0, -1)
+            self._ffn_side = torch.cuda.Stream(device=x32.device, priority=greatest if PARALLEL_FFN == 1 else least)
+            self._ffn_fork, self._ffn_done = torch.cuda.Event(), torch.cuda.Event()
+        side = self._ffn_side
+        self._ffn_fork.record(main)                   # after the norm whose output both branches read
+        side.wait_event(self._ffn_fork)
+        terms = None
+        torch.cuda.set_stream(side)
+        try:
+            if PARALLEL_FFN == 1:
+                run_mixers()
+            else:
+                terms = self.ffn.forward_parts(normed)
+            self._ffn_done.record(side)
+        finally:
+            torch.cuda.set_stream(main)
+        if PARALLEL_FFN == 1:
+            terms = self.ffn.forward_parts(normed)
+        else:
+            run_mixers()
+        main.wait_event(self._ffn_done)
+        self.ffn.add_parts(terms, x32)
+
     def _pre_norm(self, norm, x32: torch.Tensor, tag: str, step: StepInfo, cache: LayerCache) -> torch.Tensor:
         normed = scratch_buf(tag, x32.shape, self.dtype, x32.device)
         if hasattr(norm, "forward_step"):             # a norm with per-sequence state (token shift)
@@ -220,39 +266,50 @@ class Block(Part):
             self.mixer_out_norm.add_normed(y, x32)
         elif self.mixers:
             normed = self._pre_norm(self.mixer_norm, x32, "block.normed", step, cache)
-            if self.fused_in is not None:
-                proj = scratch_buf("block.proj", (x32.shape[0], self.fused_in.out_features), torch.float32, x32.device)
-                self.fused_in.forward(normed, proj)
-                parts = [proj[:, off:off + n] for off, n in self.fused_offsets]
-                if (step.max_new == 1 or PARALLEL_PROMPT_MIXERS) and x32.is_cuda and PARALLEL_MIXERS and all(hasattr(m, "mix") for m in self.mixers):
-                    self._mix_in_parallel(parts, step, cache, x32)
-                elif self.fused_out is not None:
-                    joint, views = self._joint_activations(x32)
-                    for i, (part, view) in enumerate(zip(parts, views)):
-                        self._mix(i, part, step, cache, view)
-                    self.fused_out.forward(joint, x32, accumulate=True)
-                else:
-                    for m, part in zip(self.mixers, parts):
-                        m.forward_projected(part, step, cache, x32)
-            else:
-                for m in self.mixers:
-                    m.forward(normed, step, cache, x32)
+            if self._beside(x32, step):
+                self._two_branches(normed, x32, lambda: self._run_mixers(normed, x32, step, cache))
+                return
+            self._run_mixers(normed, x32, step, cache)
         if self.parallel_ffn:
             # h was normed before the mixers added anything; the sum x + mixers(h) + ffn(h) forms in the residual stream
             self.ffn.forward(normed, x32)
         elif self.ffn is not None:
-            normed = self._pre_norm(self.ffn_norm, x32, "block.ffn_normed", step, cache)
-            if self.ffn_out_norm is None:
-                self.ffn.forward(normed, x32)
-            elif hasattr(self.ffn, "forward_parts"):
-                # a feed-forward whose result is a sum of terms hands them to the norm, which adds them up itself
-                parts, extra, gate = self.ffn.forward_parts(normed)
-                self.ffn_out_norm.add_normed(parts, x32, extra, gate)
+            self._feed_forward(x32, step, cache)
+
+    def _run_mixers(self, normed: torch.Tensor, x32: torch.Tensor, step: StepInfo, cache: LayerCache) -> None:
+        """The mixers of a layer without a mixer output norm, from their shared normed input into the residual stream."""
+        if self.fused_in is not None:
+            proj = scratch_buf("block.proj", (x32.shape[0], self.fused_in.out_features), torch.float32, x32.device)
+            self.fused_in.forward(normed, proj)
+            parts = [proj[:, off:off + n] for off, n in self.fused_offsets]
+            if (step.max_new == 1 or PARALLEL_PROMPT_MIXERS) and x32.is_cuda and PARALLEL_MIXERS and all(hasattr(m, "mix") for m in self.mixers):
+                self._mix_in_parallel(parts, step, cache, x32)
+            elif self.fused_out is not None:
+                joint, views = self._joint_activations(x32)
+                for i, (part, view) in enumerate(zip(parts, views)):
+                    self._mix(i, part, step, cache, view)
+                self.fused_out.forward(joint, x32, accumulate=True)
             else:
-                y = scratch_buf("block.ffn_out", x32.shape, torch.float32, x32.device)
-                if self._ffn_overwrites:
-                    self.ffn.forward(normed, y, accumulate=False)
-                else:
-                    y.zero_()
-                    self.ffn.forward(normed, y)
-                self.ffn_out_norm.add_normed(y, x32)
+                for m, part in zip(self.mixers, parts):
+                    m.forward_projected(part, step, cache, x32)
+        else:
+            for m in self.mixers:
+                m.forward(normed, step, cache, x32)
+
+    def _feed_forward(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache) -> None:
+        """A feed-forward with a norm of its own, after the mixers."""
+        normed = self._pre_norm(self.ffn_norm, x32, "block.ffn_normed", step, cache)
+        if self.ffn_out_norm is None:
+            self.ffn.forward(normed, x32)
+        elif hasattr(self.ffn, "forward_parts"):
+            # a feed-forward whose result is a sum of terms hands them to the norm, which adds them up itself
+            parts, extra, gate = self.ffn.forward_parts(normed)
+            self.ffn_out_norm.add_normed(parts, x32, extra, gate)
+        else:
+            y = scratch_buf("block.ffn_out", x32.shape, torch.float32, x32.device)
+            if self._ffn_overwrites:
+                self.ffn.forward(normed, y, accumulate=False)
+            else:
+                y.zero_()
+                self.ffn.forward(normed, y)
+            self.ffn_out_norm.add_normed(y, x32)

@@ -167,6 +167,11 @@ class MoEFeedForward(Part):
         self.shared.forward(normed, shared_out, accumulate=False)
         return parts, shared_out, logits[:, self.E]          # the gate's logit: whoever adds the terms takes its sigmoid
 
-    def forward(self, normed: torch.Tensor, residual: torch.Tensor, accumulate: bool = True) -> None:
-        parts, extra, gate = self.forward_parts(normed)
+    def add_parts(self, terms, residual: torch.Tensor, accumulate: bool = True) -> None:
+        """Adds what forward_parts returned into `residual` (a token's terms in the order of its choices).  A block that
+        runs this feed-forward beside its mixers computes the terms on a stream of their own and adds them here."""
+        parts, extra, gate = terms
         ops.rmsnorm_add(parts, None, 0.0, residual, extra, gate, gate_sigmoid=True, accumulate=accumulate)
+
+    def forward(self, normed: torch.Tensor, residual: torch.Tensor, accumulate: bool = True) -> None:
+        self.add_parts(self.forward_parts(normed), residual, accumulate)
